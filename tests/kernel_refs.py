@@ -19,10 +19,64 @@ class Scaled:
         self.delta, self.scale = delta, float(scale)
 
 
+class Several:
+    def __init__(self, terms):
+        self.terms = [t for t in terms if t is not None]
+
+
+def _terms_sum(delta):
+    """The 32-bit sum of what is pending (a tensor, Scaled, Several or nothing), or None."""
+    if delta is None or type(delta).__name__ == "Carried":
+        return None
+    total = None
+    for t in (delta.terms if isinstance(delta, Several) else [delta]):
+        scale = 1.0
+        if isinstance(t, Scaled):
+            t, scale = t.delta, t.scale
+        v = torch.tensor(scale, dtype=torch.float32) * t.to(torch.float32)
+        total = v if total is None else total + v
+    return total
+
+
+def sum_norm(h, delta, w1, eps, out_dtype, w2=None, rows=None, bias=None):
+    x1 = add_rmsnorm(h, _terms_sum(delta), w1, eps, out_dtype, rows=rows, bias=bias)
+    if w2 is None:
+        return x1
+    return x1, add_rmsnorm(h, None, w2, eps, out_dtype, rows=rows)
+
+
+def add_rmsnorm_pair(h, delta, w1, w2, eps1, eps2, out_dtype, bias=None):
+    x1 = sum_norm(h, delta, w1, eps1, out_dtype, bias=bias)
+    return x1, sum_norm(h, None, w2, eps2, out_dtype)
+
+
+def embed_bigram(table, bigram, ids, step, last_token, scale, buckets, mul_prev, mul_cur):
+    out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32)
+    for s in range(step.n_seqs):
+        a, b = int(step.cu_q[s]), int(step.cu_q[s + 1])
+        slot = int(step.state_slots[s])
+        for t in range(a, b):
+            tok = int(ids[t])
+            x = table[tok].to(torch.float32) * torch.tensor(scale, dtype=torch.float32)
+            if bigram is not None:
+                if int(step.positions[t]) == 0:
+                    row = buckets
+                else:
+                    prev = int(ids[t - 1]) if t > a else int(last_token[slot, 0])
+                    row = (prev * mul_prev + tok * mul_cur) % buckets
+                x = x + bigram[row].to(torch.float32)
+            out[t] = x
+        if b > a:
+            last_token[slot, 0] = int(ids[b - 1])
+    return out
+
+
 def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None, bias=None):
     scale = 1.0
     if type(delta).__name__ == "Carried":      # nothing pending
         delta = None
+    if isinstance(delta, Several):
+        delta = _terms_sum(delta)
     if isinstance(delta, Scaled):
         delta, scale = delta.delta, delta.scale
     if rows is None:
@@ -43,6 +97,8 @@ def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None, bias=None
 
 
 def residual_add(h, delta):
+    if isinstance(delta, Several):
+        delta = _terms_sum(delta)
     scale = 1.0
     if isinstance(delta, Scaled):
         delta, scale = delta.delta, delta.scale
@@ -347,11 +403,12 @@ def attention_prefill_tile_rows():
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, tile_q0, num_heads, num_kv_heads,
-                    head_dim, page_size, window, scale, out=None, sink=0.0):
+                    head_dim, page_size, window, scale, out=None, sink=0.0, keep_first=0, value_dim=None):
     T = q.shape[0]
     nq, nkv, d = num_heads, num_kv_heads, head_dim
+    dv = int(value_dim or d)
     g = nq // nkv
-    o = torch.zeros((T, nq * d), dtype=torch.float32, device=q.device)
+    o = torch.zeros((T, nq * dv), dtype=torch.float32, device=q.device)
     n = kv_lens.shape[0]
     for s in range(n):
         a, b = int(cu_q[s]), int(cu_q[s + 1])
@@ -361,6 +418,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, 
             pos = ctx + (t - a)
             lo = 0 if not window else max(0, pos - window + 1)
             js = torch.arange(lo, pos + 1, device=q.device)
+            if window and keep_first and lo > 0:      # the request's first tokens stay visible beside the window
+                js = torch.cat([torch.arange(0, min(keep_first, lo), device=q.device), js])
             pages = block_tables[s, (js // page_size)].long()
             offs = js % page_size
             K = k_cache[pages, :, offs, :].to(torch.float32)   # [keys, nkv, d]
@@ -373,7 +432,7 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, 
                     p = e / (sink * torch.exp(-sc.max()) + e.sum())
                 else:
                     p = torch.softmax(sc, dim=0)
-                o[t, h * d:(h + 1) * d] = p @ V[:, h // g, :]
+                o[t, h * dv:(h + 1) * dv] = p @ V[:, h // g, :]
     return o.to(q.dtype)
 
 
@@ -386,9 +445,11 @@ def linear_argmax(x, weight):
     return logits, argmax(logits)
 
 
-def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=0.0):
+def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=0.0,
+              keep_first=0, value_dim=None):
     return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-                           num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink)
+                           num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink, keep_first=keep_first,
+                           value_dim=value_dim)
 
 
 def patch_tokens(ids, prev, dst, src):
@@ -475,8 +536,9 @@ def relu2_(x):
 
 
 def qk_prepare(qkv, num_heads, num_kv_heads, head_dim, rot_dims, q_weight, k_weight, eps, cos, sin, positions, k_cache,
-               v_cache, slots, page_size, values_from_keys=False, write_kv=True):
+               v_cache, slots, page_size, values_from_keys=False, write_kv=True, value_dim=None):
     T, nq, nkv, d = qkv.shape[0], num_heads, num_kv_heads, head_dim
+    dv = int(value_dim or d)
     pos = positions.long()
 
     def prep(x, w):                                        # [T, heads, d] float32
@@ -487,11 +549,12 @@ def qk_prepare(qkv, num_heads, num_kv_heads, head_dim, rot_dims, q_weight, k_wei
         return x
 
     q = qkv[:, :nq * d].to(torch.float32).reshape(T, nq, d)
-    k_raw = qkv[:, nq * d:(nq + nkv) * d].to(torch.float32).reshape(T, nkv, d)
     qn = prep(q, q_weight)
     if write_kv:
+        k_raw = qkv[:, nq * d:(nq + nkv) * d].to(torch.float32).reshape(T, nkv, d)
         kn = prep(k_raw, k_weight)
-        v = k_raw if values_from_keys else qkv[:, (nq + nkv) * d:(nq + 2 * nkv) * d].to(torch.float32).reshape(T, nkv, d)
+        v = k_raw if values_from_keys else \
+            qkv[:, (nq + nkv) * d:(nq + nkv) * d + nkv * dv].to(torch.float32).reshape(T, nkv, dv)
         for t in range(T):
             slot = int(slots[t])
             if slot < 0:
@@ -577,14 +640,15 @@ def head_norm_gate(o, weight, eps, gate, gate_kind, heads, vdim, out_dtype):
     return (x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight * act).reshape(T, heads * vdim).to(out_dtype)
 
 
-def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False):
+def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False, correction=None):
     T, NR = logits.shape
     s = torch.sigmoid(logits) if score == "sigmoid" else torch.softmax(logits, dim=-1)
+    c = s if correction is None else s + correction          # what is compared; the weights stay uncorrected
     per = NR // groups
-    gscore = s.reshape(T, groups, per).topk(min(2, per), dim=-1).values.sum(-1)
+    gscore = c.reshape(T, groups, per).topk(min(2, per), dim=-1).values.sum(-1)
     best = gscore.topk(keep, dim=-1).indices
     allowed = torch.zeros((T, groups), dtype=torch.bool).scatter_(1, best, True).repeat_interleave(per, dim=1)
-    pick = torch.where(allowed, s, torch.full_like(s, -float("inf")))
+    pick = torch.where(allowed, c, torch.full_like(c, -float("inf")))
     chosen = pick.topk(top, dim=-1).indices
     weight = s.gather(1, chosen)
     if renormalize:
@@ -592,5 +656,6 @@ def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0,
     return chosen.to(torch.int32), (weight * scale).to(torch.float32)
 
 
-def moe_router_grouped(x, w_router, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False):
-    return moe_route_grouped(x.to(torch.float32) @ w_router.to(torch.float32).T, top, score, groups, keep, scale, renormalize)
+def moe_router_grouped(x, w_router, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False, correction=None):
+    return moe_route_grouped(x.to(torch.float32) @ w_router.to(torch.float32).T, top, score, groups, keep, scale, renormalize,
+                             correction)

@@ -1,10 +1,10 @@
 """The cache manager: which pages and which state slot each request holds.
 
 Keys and values live in pages of ``page_size`` tokens.  Caches with the same need
-(kv heads, head size, window, with or without values) form a *group*: a group has a page pool of its own
+(kv heads, key and value size, window and kept first tokens, with or without values) form a *group*: a group has a page pool of its own
 and one block table per request, valid for every cache of the group.  A request's
 pages are given back when it ends, and, in a group with a window, as soon as the
-window has passed them.  Beside the pages, each request holds one slot for
+window has passed them (except those that hold the first tokens the group keeps visible).  Beside the pages, each request holds one slot for
 per-request state of fixed size (used by mixers that keep a state instead of keys;
 Qwen3 has none, the slot is still allocated and freed).
 
@@ -35,6 +35,8 @@ class KVNeedKey:
     head_dim: int
     window: Optional[int]
     values: bool = True        # False: pages of keys only
+    value_dim: Optional[int] = None   # size of a value where it differs from a key's
+    keep_first: int = 0        # with a window: the request's first tokens whose pages are never given back
 
 
 @dataclass
@@ -82,9 +84,14 @@ class CacheManager:
         sizes: list[int] = []
         self.group_of: dict[str, tuple[int, int]] = {}   # cache name -> (group, index within the group)
         for name, need in kv_needs.items():
-            key = KVNeedKey(need.num_kv_heads, need.head_dim, need.window, getattr(need, "values", True))
+            vd = getattr(need, "value_dim", None)
+            key = KVNeedKey(need.num_kv_heads, need.head_dim, need.window, getattr(need, "values", True),
+                            None if vd is None or vd == need.head_dim else int(vd),
+                            int(getattr(need, "keep_first", 0) or 0) if need.window is not None else 0)
             if key.window is not None and key.window <= 0:
                 raise ValueError(f"cache {name!r}: window must be positive")
+            if key.keep_first < 0:
+                raise ValueError(f"cache {name!r}: the kept first tokens cannot be fewer than none")
             if key in keys:
                 gi = keys.index(key)
                 self.group_of[name] = (gi, len(members[gi]))
@@ -103,6 +110,9 @@ class CacheManager:
         self._handle = self._lib.zi_cache_create(n, windows, pages, page_size, max_requests)
         if not self._handle:
             raise ValueError("the cache manager could not be created")
+        for gi, k in enumerate(keys):
+            if k.keep_first:
+                self._lib.zi_cache_keep_first(self._handle, gi, k.keep_first)
         self.groups: list[KVGroup] = [
             KVGroup(key, names, GroupPool(self._handle, gi, f"kv pages of group {gi}"))
             for gi, (key, names) in enumerate(zip(keys, members))]

@@ -2,7 +2,8 @@
 
 One page of a group holds ``page_size`` tokens of keys and of values for every
 cache of the group: ``caches * 2 * kv heads * page_size * head_dim * element size``
-bytes (half of that in a group that keeps keys only).  Every group gets the same number of pages, so one page id across all groups
+bytes (half of that in a group that keeps keys only; with values of another size than the keys, key size plus
+value size in place of twice the head size).  Every group gets the same number of pages, so one page id across all groups
 costs the sum of those.  The reference sizes one contiguous cache per request by
 the same product over its layers
 (src/model/runtime/optimized_kv_cache/cache.zig:423-456) and prints it with its
@@ -14,13 +15,16 @@ from typing import Optional
 
 
 def group_shapes(kv_needs: dict) -> list[tuple[int, int, int, int]]:
-    """(caches, kv heads, head size, planes) per group, grouping equal needs like the manager does;
-    planes is 2 (keys and values) or 1 (keys only)."""
+    """(caches, kv heads, elements per token and kv head, 1) per group, grouping equal needs like the manager
+    does; the elements are key size plus value size (the key size alone in a group that keeps keys only)."""
     groups: dict[tuple, int] = {}
     for need in kv_needs.values():
-        key = (need.num_kv_heads, need.head_dim, need.window, 2 if getattr(need, "values", True) else 1)
+        values = getattr(need, "values", True)
+        vd = getattr(need, "value_dim", None) or need.head_dim
+        keep = (getattr(need, "keep_first", 0) or 0) if need.window is not None else 0
+        key = (need.num_kv_heads, need.head_dim, need.window, values, vd if values else 0, keep)
         groups[key] = groups.get(key, 0) + 1
-    return [(n, key[0], key[1], key[3]) for key, n in groups.items()]
+    return [(n, key[0], key[1] + key[4], 1) for key, n in groups.items()]
 
 
 def bytes_per_page(kv_needs: dict, page_size: int, element_size: int) -> int:

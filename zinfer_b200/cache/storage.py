@@ -2,7 +2,9 @@
 
 For each group one tensor ``[caches, 2, pages, kv heads, page_size, head_dim]``
 (keys at index 0, values at index 1; ``[caches, 1, ...]`` for a group that keeps keys
-only) in the run's dtype: a page id is valid for every cache of the group.  For each state cache one tensor
+only) in the run's dtype: a page id is valid for every cache of the group.  In a group whose values have another
+size than its keys, the values lie in a tensor of their own, ``[caches, 1, pages, kv heads, page_size, value_dim]``.
+For each state cache one tensor
 ``[request slots + 1, *shape]``, zeroed for a slot when a request takes it.  The last
 slot belongs to no request: the rows that pad a captured decode batch name it, so a
 mixer that updates ``state[state_slots]`` with device operations alone harms nobody.
@@ -41,10 +43,14 @@ class CacheStorage:
     def __init__(self, manager: CacheManager, state_needs: dict, dtype: torch.dtype, device):
         self.manager = manager
         self.kv: list[torch.Tensor] = []
+        self.kv_values: list[Optional[torch.Tensor]] = []     # per group: the values' own tensor, where they need one
         for g in manager.groups:
-            shape = (len(g.caches), 2 if g.key.values else 1, g.pool.num_pages, g.key.num_kv_heads, manager.page_size,
-                     g.key.head_dim)
+            vd = getattr(g.key, "value_dim", None)
+            apart = g.key.values and vd is not None and vd != g.key.head_dim
+            shape = (len(g.caches), 2 if g.key.values and not apart else 1, g.pool.num_pages, g.key.num_kv_heads,
+                     manager.page_size, g.key.head_dim)
             self.kv.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.kv_values.append(torch.zeros((*shape[:1], 1, *shape[2:5], vd), dtype=dtype, device=device) if apart else None)
         self.state: dict[str, torch.Tensor] = {
             name: torch.zeros((manager.max_requests + 1, *need.shape), dtype=need.dtype, device=device)
             for name, need in state_needs.items()
@@ -52,9 +58,9 @@ class CacheStorage:
 
     def kv_view(self, cache_name: str, writes: bool) -> KVCacheView:
         gi, ci = self.manager.group_of[cache_name]
-        t = self.kv[gi]
-        return KVCacheView(k=t[ci, 0], v=t[ci, 1] if t.shape[1] > 1 else None, group=gi,
-                           page_size=self.manager.page_size, writes=writes)
+        t, tv = self.kv[gi], self.kv_values[gi]
+        v = tv[ci, 0] if tv is not None else (t[ci, 1] if t.shape[1] > 1 else None)
+        return KVCacheView(k=t[ci, 0], v=v, group=gi, page_size=self.manager.page_size, writes=writes)
 
     def state_view(self, cache_name: str, writes: bool = True) -> StateView:
         return StateView(self.state[cache_name], writes)
@@ -70,7 +76,10 @@ class CacheStorage:
         self.kv[group][:, 0].index_fill_(1, idx, value)
         if self.kv[group].shape[1] > 1:
             self.kv[group][:, 1].index_fill_(1, idx, -value)
+        if self.kv_values[group] is not None:
+            self.kv_values[group][:, 0].index_fill_(1, idx, -value)
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \
+            sum(t.numel() * t.element_size() for t in self.kv_values if t is not None) + \
             sum(t.numel() * t.element_size() for t in self.state.values())

@@ -13,6 +13,12 @@ const char* zi_last_error();
 
 int zi_embed_gather(float* h, const void* table, int table_dtype, const int* ids, int T, int H, int V,
                     cudaStream_t stream);
+// h[t] = scale * table[ids[t]] + bigram[row], row = (previous token * mul_prev + token * mul_cur) mod buckets, or row
+// `buckets` for a request's first token (position 0).  The token before a step's first token of a request comes from
+// last_token[state_slots[request]], which is then set to the request's last token of this step.
+int zi_embed_bigram(float* h, const void* table, const void* bigram, int table_dtype, const int* ids, const int* positions,
+                    const int* cu_q, const int* state_slots, int* last_token, int n_seqs, int T, int H, int V, float scale,
+                    int buckets, long long mul_prev, long long mul_cur, cudaStream_t stream);
 int zi_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_partials, int splits,
                    long long split_stride, const float* w, float eps, void* out, int out_dtype, const int* rows,
                    int n_rows, int H, cudaStream_t stream);
@@ -117,17 +123,34 @@ int zi_paged_attention_sink(void* out, int out_stride, const void* q, int q_stri
                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                             int d, int dv, int v_row, int page_size, int window, float scale, int skip_from,
                             int skip_single, float sink, cudaStream_t stream);
+// The general form: values of any size dv, and with a window the first keep_first tokens of a request stay visible.
+int zi_paged_attention_mask(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
+                            const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                            const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                            int d, int dv, int v_row, int page_size, int window, int keep_first, float scale,
+                            int skip_from, int skip_single, float sink, cudaStream_t stream);
 // q/k norm, rotation of the first rot_dims dimensions of a head, page write; values of their own or the keys as projected.
 int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv, int d,
                   int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t, const float* sin_t,
                   int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
                   int v_from_k, int write_kv, cudaStream_t stream);
+// The same with value heads of dv elements (rows [q heads of d | k heads of d | v heads of dv]).
+int zi_qk_prepare_v(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv, int d,
+                    int dv, int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t, const float* sin_t,
+                    int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
+                    int v_from_k, int write_kv, cudaStream_t stream);
 int zi_rope_table_scaled(float* cos_t, float* sin_t, int n_pos, int d, float theta, float factor, cudaStream_t stream);
 // h += norm(sa * a + sb * b) * w (the norm of a sublayer's output), x_out = h in the activations' type; a and b whole
 // or as split-K partial sums [splits][T][H].
 int zi_norm_residual(float* h, const void* a, int a_dtype, const float* a_part, int a_splits, long long a_zstride, float sa,
                      const void* b, int b_dtype, const float* b_part, int b_splits, long long b_zstride, float sb,
                      const float* w, float eps, void* x_out, int out_dtype, int T, int H, cudaStream_t stream);
+// h += sum of up to four updates (whole or split-K partial sums, each with a multiplier) + bias; out1 = norm(h) * w1 and,
+// with w2, out2 = norm(h) * w2 (both norms share the root mean square).  With rows: picked rows, h unchanged.
+int zi_sum_norm_pair(float* h, int n_terms, const void* const* whole, const int* dtypes, const float* const* part,
+                     const int* splits, const long long* zstride, const float* scales, const float* bias, const float* w1,
+                     const float* w2, float eps, void* out1, void* out2, int out_dtype, const int* rows, int n_rows, int H,
+                     cudaStream_t stream);
 int zi_cast_rows(void* out, int out_dtype, const float* h, long long n, cudaStream_t stream);
 int zi_relu2(void* x, int dtype, long long n, cudaStream_t stream);
 // Mixers with a matrix-valued state per head (linear attention with decays, with or without the delta rule).
@@ -151,6 +174,12 @@ int zi_moe_router_grouped(int* chosen, float* weight, const void* x, int x_dtype
                           cudaStream_t stream);
 int zi_moe_route_grouped(int* chosen, float* weight, const float* logits, int T, int NR, int top, int renormalize,
                          int score_kind, int groups, int keep, float wscale, cudaStream_t stream);
+// The same two with a correction [NR] added to the scores for the choice only (null: none).
+int zi_moe_router_grouped_c(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                            const float* correction, int T, int K, int NR, int top, int renormalize, int score_kind,
+                            int groups, int keep, float wscale, cudaStream_t stream);
+int zi_moe_route_grouped_c(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
+                           int renormalize, int score_kind, int groups, int keep, float wscale, cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
 int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
                       const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,

@@ -1,6 +1,7 @@
 // Causal attention of query tokens against the paged cache, for any mix of prompt
 // portions and single decoded tokens, any head size up to 256 in steps of 2, any
-// number of heads and groups, with an optional window.  32-bit arithmetic on the
+// number of heads and groups, with an optional window that may also keep a request's
+// first tokens visible (keep_first).  32-bit arithmetic on the
 // CUDA cores (exact expf); the storage type alone differs between the float32 path
 // and the plain bfloat16 path.  A query row visits its keys in ascending order in
 // tiles aligned to multiples of BK, so its result does not depend on how the
@@ -15,9 +16,10 @@
 namespace {
 constexpr int BQ = 16, BK = 32, THREADS = 128, ROWS_PER_WARP = BQ / (THREADS / 32);
 
-// Values may be narrower than keys and may lie in the key rows themselves (a latent cache whose row
+// Values may have another size than keys and may lie in the key rows themselves (a latent cache whose row
 // serves as key and, in its first dv columns, as value): dv value columns are read from rows of
 // v_row elements in `vcache`; the output has dv columns per head.  MAXJ * 32 bounds dv.
+// With a window, query i sees key j <= i if i - j < window or j < keep_first.
 template <typename T, int MAXJ>
 __global__ void __launch_bounds__(THREADS)
 paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride,
@@ -25,7 +27,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
-                       float scale, int dv, int v_row, int skip_from, int skip_single, float sink) {
+                       float scale, int dv, int v_row, int skip_from, int skip_single, float sink, int keep_first) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -43,6 +45,8 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
   const int first_pos = ctx + q0, last_pos = first_pos + nqv - 1;
   const int kv_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
   const int kv_end = last_pos + 1;
+  // keys [0, keep_end) lie before the window and stay visible; the tiles between them and the window are skipped
+  const int keep_end = window > 0 ? min(keep_first, kv_begin) : 0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* bt = block_tables + (size_t)seq * bt_stride;
 
@@ -60,22 +64,31 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
     for (int j = 0; j < MAXJ; ++j) acc[i][j] = 0.f;
   }
 
-  for (int kt = (kv_begin / BK) * BK; kt < kv_end; kt += BK) {
+  for (int kt = keep_end > 0 ? 0 : (kv_begin / BK) * BK; kt < kv_end; kt += BK) {
+    if (kt >= keep_end && kt + BK <= kv_begin) {   // a tile wholly between the kept first tokens and the window
+      kt = (kv_begin / BK) * BK - BK;
+      continue;
+    }
     __syncthreads();  // previous tile fully consumed (also orders the Q load the first time)
     for (int e = tid; e < BK * d; e += THREADS) {
       const int kk = e / d, c = e % d;
       const int j = kt + kk;
-      float kval = 0.f, vval = 0.f;
-      if (j >= kv_begin && j < kv_end) {
+      float kval = 0.f;
+      if ((j >= kv_begin || j < keep_end) && j < kv_end) {
         const int page = bt[j / page_size];
-        if (page >= 0) {
-          const size_t r = ((size_t)page * nkv + kvh) * page_size + (j % page_size);
-          kval = to_f32(kcache[r * d + c]);
-          if (c < dv) vval = to_f32(vcache[r * v_row + c]);
-        }
+        if (page >= 0) kval = to_f32(kcache[(((size_t)page * nkv + kvh) * page_size + (j % page_size)) * d + c]);
       }
       Ks[kk * (d + 1) + c] = kval;
-      if (c < dv) Vs[kk * dv + c] = vval;
+    }
+    for (int e = tid; e < BK * dv; e += THREADS) {
+      const int kk = e / dv, c = e % dv;
+      const int j = kt + kk;
+      float vval = 0.f;
+      if ((j >= kv_begin || j < keep_end) && j < kv_end) {
+        const int page = bt[j / page_size];
+        if (page >= 0) vval = to_f32(vcache[(((size_t)page * nkv + kvh) * page_size + (j % page_size)) * v_row + c]);
+      }
+      Vs[e] = vval;
     }
     __syncthreads();
 
@@ -91,7 +104,7 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
       float s = 0.f;
       for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
       s *= scale;
-      const bool visible = j <= pos && j >= kv_begin && (window <= 0 || j > pos - window);
+      const bool visible = j <= pos && (window <= 0 || j > pos - window || j < keep_first);
       if (!visible) s = -INFINITY;
       const float m_new = fmaxf(m[i], warp_max(s));
       float p = 0.f;
@@ -162,11 +175,25 @@ extern "C" int zi_paged_attention_sink(void* out, int out_stride, const void* q,
                                        const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
                                        float scale, int skip_from, int skip_single, float sink, cudaStream_t stream) {
+  return zi_paged_attention_mask(out, out_stride, q, q_stride, dtype, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                                 tile_seq, tile_q0, n_tiles, nq, nkv, d, dv, v_row, page_size, window, 0, scale, skip_from,
+                                 skip_single, sink, stream);
+}
+
+// The general form: a sink, values of any size (dv columns of rows of v_row elements), and a window that
+// keeps the first keep_first tokens of a request visible.
+extern "C" int zi_paged_attention_mask(void* out, int out_stride, const void* q, int q_stride, int dtype,
+                                       const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                                       const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
+                                       int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
+                                       int keep_first, float scale, int skip_from, int skip_single, float sink,
+                                       cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (keep_first < 0) return zi_refuse("paged_attention: %d kept first tokens", keep_first);
   if (!(sink >= 0.f)) return zi_refuse("paged_attention: the sink's weight must not be negative");
   constexpr int WIDE = 20;   // value columns up to 640 (latent caches); 8 serves every ordinary head size
   if (d <= 0 || d > 32 * WIDE) return zi_refuse("paged_attention: head_dim %d is outside 1..%d", d, 32 * WIDE);
-  if (dv <= 0 || dv > d || v_row < dv) return zi_refuse("paged_attention: %d value columns of rows of %d, keys of %d", dv, v_row, d);
+  if (dv <= 0 || dv > 32 * WIDE || v_row < dv) return zi_refuse("paged_attention: %d value columns of rows of %d, keys of %d", dv, v_row, d);
   if (nkv <= 0 || nq % nkv) return zi_refuse("paged_attention: %d query heads do not divide into %d kv heads", nq, nkv);
   if (page_size <= 0) return zi_refuse("paged_attention: page_size %d", page_size);
   const size_t smem = (size_t)(BQ * d + BK * (d + 1) + BK * dv + BQ * BK) * sizeof(float);
@@ -180,7 +207,7 @@ extern "C" int zi_paged_attention_sink(void* out, int out_stride, const void* q,
     }                                                                                                              \
     zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride,         \
               (const TT*)kcache, (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, \
-              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single, sink);                          \
+              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single, sink, keep_first);              \
   } while (0)
   ZI_DISPATCH_DTYPE(dtype, TT, {
     if (dv <= 256) ZI_LAUNCH_ATTN(8);

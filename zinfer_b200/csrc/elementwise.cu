@@ -30,6 +30,64 @@ extern "C" int zi_embed_gather(float* h, const void* table, int table_dtype, con
   return zi_check_launch("embed_gather");
 }
 
+// ------------------------------------------- embedding with a hashed table of token pairs
+// One block per token.  The token before: the one before it in this step's portion, or, for the portion's first
+// token, what the request's slot holds from the step before (nothing at position 0: the table's last row).  The
+// block of a portion's first token reads the slot and then stores the portion's last token there, so no other
+// block touches the slot.
+template <typename T>
+__global__ void embed_bigram_kernel(float* __restrict__ h, const T* __restrict__ table, const T* __restrict__ bigram,
+                                    const int* __restrict__ ids, const int* __restrict__ positions,
+                                    const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                                    int* __restrict__ last_token, int n_seqs, int H, int V, float scale, int buckets,
+                                    long long mul_prev, long long mul_cur) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int lo = 0, hi = n_seqs - 1;                 // the request whose portion holds token t
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int start = cu_q[lo], end = cu_q[lo + 1];
+  const int id = ids[t];
+  int prev = -1;
+  if (positions[t] > 0) prev = t > start ? ids[t - 1] : last_token[state_slots[lo]];
+  __syncthreads();                             // every thread has read the slot before it is overwritten
+  if (t == start && threadIdx.x == 0 && end > start) last_token[state_slots[lo]] = ids[end - 1];
+  float* out = h + (size_t)t * H;
+  if (id < 0 || id >= V) {  // the host refuses such ids; never read out of bounds
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * H;
+  if (bigram == nullptr) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
+    return;
+  }
+  long long r = buckets;
+  if (prev >= 0) {
+    r = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    if (r < 0) r += buckets;
+  }
+  const T* pair = bigram + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = fmaf(to_f32(row[i]), scale, to_f32(pair[i]));
+}
+
+extern "C" int zi_embed_bigram(float* h, const void* table, const void* bigram, int table_dtype, const int* ids,
+                               const int* positions, const int* cu_q, const int* state_slots, int* last_token, int n_seqs,
+                               int T, int H, int V, float scale, int buckets, long long mul_prev, long long mul_cur,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_seqs <= 0 || !cu_q || !state_slots || !last_token || !positions)
+    return zi_refuse("embed_bigram: the step's request arrays and the slots of the last tokens are needed");
+  if (bigram && buckets <= 0) return zi_refuse("embed_bigram: %d buckets", buckets);
+  ZI_DISPATCH_DTYPE(table_dtype, TT,
+                    zi_launch(embed_bigram_kernel<TT>, dim3(T), dim3(256), 0, stream, h, (const TT*)table, (const TT*)bigram, ids,
+                              positions, cu_q, state_slots, last_token, n_seqs, H, V, scale, buckets, mul_prev, mul_cur));
+  return zi_check_launch("embed_bigram");
+}
+
 // ------------------------------------------------------------ residual add + RMSNorm
 // h[row] += delta[row] (when delta is given), out[r] = h[row] * w / sqrt(mean(h[row]^2) + eps).
 // With `rows` (a gather of picked rows, possibly with repeats) h itself is not modified.
@@ -773,7 +831,8 @@ __global__ void qk_prepare_kernel(const T* src, int src_stride, T* q_out, int q_
                                   int rot_dims, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_table_pos,
                                   const int* __restrict__ positions, T* __restrict__ kcache, T* __restrict__ vcache,
-                                  const int* __restrict__ slots, int page_size, int v_from_k, int write_kv, int T_) {
+                                  const int* __restrict__ slots, int page_size, int v_from_k, int write_kv, int T_,
+                                  int dv) {
   pdl_launch_dependents();
   pdl_wait();
   const int n_heads = nq + (write_kv ? (v_from_k ? nkv : 2 * nkv) : 0);
@@ -781,6 +840,15 @@ __global__ void qk_prepare_kernel(const T* src, int src_stride, T* q_out, int q_
   if (wi >= T_ * n_heads) return;
   const int t = wi / n_heads, head = wi % n_heads;
   const T* x = src + (size_t)t * src_stride + (size_t)head * d;
+  if (head >= nq + nkv) {              // a value head of its own (dv elements, behind all key heads): copy
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int kvh = head - nq - nkv;
+    const T* xv = src + (size_t)t * src_stride + (size_t)(nq + nkv) * d + (size_t)kvh * dv;
+    const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * dv;
+    for (int i = lane; i < dv; i += 32) vcache[at + i] = xv[i];
+    return;
+  }
   T* dst;
   T* vdst = nullptr;
   if (head < nq) {
@@ -790,10 +858,6 @@ __global__ void qk_prepare_kernel(const T* src, int src_stride, T* q_out, int q_
     if (slot < 0) return;
     const int kvh = (head - nq) % nkv;
     const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (slot % page_size)) * d;
-    if (head >= nq + nkv) {            // a value head of its own: copy
-      for (int i = lane; i < d; i += 32) vcache[at + i] = x[i];
-      return;
-    }
     dst = kcache + at;
     if (v_from_k) vdst = vcache + at;
   }
@@ -830,7 +894,16 @@ extern "C" int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, 
                              int d, int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t,
                              const float* sin_t, int n_table_pos, const int* positions, void* kcache, void* vcache,
                              const int* slots, int page_size, int v_from_k, int write_kv, cudaStream_t stream) {
+  return zi_qk_prepare_v(src, dtype, T, src_stride, q_out, q_stride, nq, nkv, d, d, rot_dims, qw, kw, eps, cos_t, sin_t,
+                         n_table_pos, positions, kcache, vcache, slots, page_size, v_from_k, write_kv, stream);
+}
+
+extern "C" int zi_qk_prepare_v(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv,
+                               int d, int dv, int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t,
+                               const float* sin_t, int n_table_pos, const int* positions, void* kcache, void* vcache,
+                               const int* slots, int page_size, int v_from_k, int write_kv, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (dv <= 0 || (v_from_k && dv != d)) return zi_refuse("qk_prepare: values of %d elements beside keys of %d", dv, d);
   if (d <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > d)
     return zi_refuse("qk_prepare: %d rotated dimensions of a head of %d", rot_dims, d);
   if ((cos_t == nullptr) != (sin_t == nullptr)) return zi_refuse("qk_prepare: cos and sin tables go together");
@@ -841,7 +914,7 @@ extern "C" int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, 
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(qk_prepare_kernel<TT>, dim3(blocks), dim3(warps * 32), 0, stream, (const TT*)src,
                                          src_stride, (TT*)q_out, q_stride, nq, nkv, d, cos_t ? rot_dims : 0, qw, kw, eps, cos_t,
                                          sin_t, n_table_pos, positions, (TT*)kcache, (TT*)vcache, slots, page_size, v_from_k,
-                                         write_kv, T));
+                                         write_kv, T, dv));
   return zi_check_launch("qk_prepare");
 }
 
@@ -862,6 +935,100 @@ __device__ __forceinline__ float operand_at(const TA* a, const float* ap, int as
   }
   for (; z < as; ++z) v += p[(size_t)z * az];
   return v;
+}
+
+// ------------------------- several updates into the residual stream, then one or two norms of it
+// h[row] += sum_i scale_i * term_i[row] (+ bias), in the order of the terms; out1 = h * w1 / rms(h), and with w2 also
+// out2 = h * w2 / rms(h): two norms of the same row share their root mean square (a block whose two sublayers
+// read the same stream).  A term comes whole (float32 or bfloat16) or as split-K partial sums [splits][T][H] added
+// in order.  With `rows` (picked rows, repeats allowed) h is left as it is.  One block per row, which it keeps in
+// shared memory, so every operand is read once; 32-bit throughout.
+struct SumTerm {
+  const void* whole;
+  const float* part;
+  int dtype, splits;
+  long long zstride;
+  float scale;
+};
+struct SumTerms {
+  SumTerm t[4];
+  int n;
+};
+
+__device__ __forceinline__ float sum_term_at(const SumTerm& t, size_t at) {
+  if (t.part) return operand_at((const float*)nullptr, t.part, t.splits, (size_t)t.zstride, at);
+  return t.dtype == ZI_BF16 ? to_f32(((const __nv_bfloat16*)t.whole)[at]) : ((const float*)t.whole)[at];
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+sum_norm_pair_kernel(float* __restrict__ h, SumTerms terms, const float* __restrict__ bias, const float* __restrict__ w1,
+                     const float* __restrict__ w2, float eps, TO* __restrict__ out1, TO* __restrict__ out2,
+                     const int* __restrict__ rows, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  extern __shared__ float ys[];
+  const int r = blockIdx.x;
+  const size_t row = (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.f;
+  for (int c0 = threadIdx.x; c0 < H; c0 += 4 * blockDim.x) {
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {      // four columns of a thread at a time: their loads are in flight together
+      const int c = c0 + u * blockDim.x;
+      v[u] = 0.f;
+      if (c < H) {
+        v[u] = h[row + c];
+        for (int i = 0; i < terms.n; ++i) v[u] = fmaf(terms.t[i].scale, sum_term_at(terms.t[i], row + c), v[u]);
+        if (bias) v[u] += bias[c];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * blockDim.x;
+      if (c < H) {
+        ys[c] = v[u];
+        if (!rows && (terms.n > 0 || bias)) h[row + c] = v[u];
+        ss = fmaf(v[u], v[u], ss);
+      }
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o1 = out1 + (size_t)r * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) o1[c] = from_f32<TO>(ys[c] * w1[c] * inv);
+  if (w2) {
+    TO* o2 = out2 + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o2[c] = from_f32<TO>(ys[c] * w2[c] * inv);
+  }
+}
+
+// terms: n_terms entries of (whole, dtype, part, splits, zstride, scale), given as parallel arrays on the host.
+extern "C" int zi_sum_norm_pair(float* h, int n_terms, const void* const* whole, const int* dtypes, const float* const* part,
+                                const int* splits, const long long* zstride, const float* scales, const float* bias,
+                                const float* w1, const float* w2, float eps, void* out1, void* out2, int out_dtype,
+                                const int* rows, int n_rows, int H, cudaStream_t stream) {
+  if (n_rows <= 0 || H <= 0) return 0;
+  if (n_terms < 0 || n_terms > 4) return zi_refuse("sum_norm_pair: %d updates (at most 4)", n_terms);
+  if (!w1 || !out1 || (w2 && !out2)) return zi_refuse("sum_norm_pair: a norm needs its weight and its output");
+  SumTerms terms = {};
+  terms.n = n_terms;
+  for (int i = 0; i < n_terms; ++i) {
+    if ((whole[i] == nullptr) == (part[i] == nullptr)) return zi_refuse("sum_norm_pair: give update %d either whole or as partial sums", i);
+    if (whole[i] && dtypes[i] != ZI_F32 && dtypes[i] != ZI_BF16) return zi_refuse("sum_norm_pair: unknown dtype tag %d", dtypes[i]);
+    terms.t[i] = SumTerm{whole[i], part[i], dtypes[i], splits[i], zstride[i], scales[i]};
+  }
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return zi_refuse("sum_norm_pair: rows of %d values are more than this kernel holds", H);
+  const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : 256);
+  ZI_DISPATCH_DTYPE(out_dtype, TO, {
+    auto kern = sum_norm_pair_kernel<TO>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return zi_refuse("sum_norm_pair: cannot get %zu bytes of shared memory", smem);
+    zi_launch(kern, dim3(n_rows), dim3(threads), smem, stream, h, terms, bias, w1, w2, eps, (TO*)out1, (TO*)out2, rows, H);
+  });
+  return zi_check_launch("sum_norm_pair");
 }
 
 // Many rows (a prompt): the GPU is full of rows, a block of 256 threads reads its row's update twice (the second time

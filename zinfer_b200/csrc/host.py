@@ -22,6 +22,7 @@ _SIGNATURES = {
     "zi_pool_stats": (None, [_P, _P]),
     "zi_pool_check": (_I, [_P]),
     "zi_cache_create": (_P, [_I, _P, _P, _I, _I]),
+    "zi_cache_keep_first": (_I, [_P, _I, _I]),
     "zi_cache_destroy": (None, [_P]),
     "zi_cache_add": (_I, [_P, _LL]),
     "zi_cache_free": (_I, [_P, _LL, _P, _I]),

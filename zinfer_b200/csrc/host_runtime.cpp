@@ -103,6 +103,7 @@ struct Pool {
 
 struct Group {
   int window = 0;   // 0: every key stays visible
+  int keep_first = 0;   // with a window: this many tokens at a request's start stay visible too
   Pool pool;
 };
 
@@ -185,6 +186,14 @@ extern "C" void* zi_cache_create(int n_groups, const int* windows, const int* nu
   return c;
 }
 extern "C" void zi_cache_destroy(void* h) { delete as_cache(h); }
+
+// A group whose window also keeps a request's first `tokens` tokens visible: their pages stay.
+extern "C" int zi_cache_keep_first(void* h, int group, int tokens) {
+  Cache* c = as_cache(h);
+  if (group < 0 || group >= (int)c->groups.size() || tokens < 0) return ERR_ARGUMENT;
+  c->groups[group].keep_first = tokens;
+  return 0;
+}
 
 // The request's state slot, or a negative code.
 extern "C" int zi_cache_add(void* h, long long id) {
@@ -317,7 +326,8 @@ extern "C" int zi_cache_commit(void* h, long long id, long long n_new, int* rele
     const long long first_needed = r->length - window + 1;
     const long long n_dead = first_needed > 0 ? first_needed / c->page_size : 0;
     std::vector<int>& table = r->tables[g];
-    for (long long b = 0; b < n_dead && b < (long long)table.size(); ++b) {
+    const long long kept = c->blocks_for(c->groups[g].keep_first);   // blocks that hold tokens every query still reads
+    for (long long b = kept; b < n_dead && b < (long long)table.size(); ++b) {
       if (table[b] < 0) continue;
       const int p = table[b];
       if (c->groups[g].pool.release(&p, 1, &bad) != 0) return zi_refuse("page %d of group %zu is not in use", p, g), ERR_CHECK;

@@ -83,12 +83,13 @@ __device__ __forceinline__ void route_token(int* __restrict__ chosen, float* __r
 // The choice among groups of neighbouring outputs: scores are sigmoid(z) (score_kind 1) or a softmax (0); the
 // outputs form `groups` equal groups, a group's score is the sum of its two largest scores, and only outputs
 // of the `keep` best groups can be chosen; the weight of a chosen output is its score times wscale, divided
-// by the chosen scores' sum first if `renormalize`.  Ties go to the lower index.  score, pick, gsc: NR floats
-// each of shared memory for this warp.
+// by the chosen scores' sum first if `renormalize`.  Ties go to the lower index.  A correction [NR], when given,
+// is added to the scores wherever they are compared (groups and outputs), never to the weights.  score, pick,
+// gsc: NR floats each of shared memory for this warp.
 __device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, float* __restrict__ weight, const float* z,
                                                     float* score, float* pick, float* gsc, int t, int NR, int top,
                                                     int renormalize, int score_kind, int groups, int keep,
-                                                    float wscale, int lane) {
+                                                    float wscale, int lane, const float* __restrict__ corr = nullptr) {
   if (score_kind == 1) {
     for (int j = lane; j < NR; j += 32) score[j] = 1.0f / (1.0f + expf(-z[j]));
   } else {
@@ -110,7 +111,7 @@ __device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, fl
   for (int g = lane; g < groups; g += 32) {      // the two largest scores of the group
     float a = -INFINITY, b = -INFINITY;
     for (int i = 0; i < per; ++i) {
-      const float v = score[g * per + i];
+      const float v = score[g * per + i] + (corr ? corr[g * per + i] : 0.f);
       if (v > a) { b = a; a = v; }
       else if (v > b) b = v;
     }
@@ -133,7 +134,7 @@ __device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, fl
       if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
     }
     if (arg == 0x7fffffff) break;                // uniform: nothing is left
-    for (int i = lane; i < per; i += 32) pick[arg * per + i] = score[arg * per + i];
+    for (int i = lane; i < per; i += 32) pick[arg * per + i] = score[arg * per + i] + (corr ? corr[arg * per + i] : 0.f);
     if (lane == 0) gsc[arg] = -INFINITY;
     __syncwarp();
   }
@@ -169,7 +170,8 @@ __device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, fl
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_grouped_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits, int T,
-                         int NR, int top, int renormalize, int score_kind, int groups, int keep, float wscale) {
+                         int NR, int top, int renormalize, int score_kind, int groups, int keep, float wscale,
+                         const float* __restrict__ correction) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -178,7 +180,7 @@ moe_route_grouped_kernel(int* __restrict__ chosen, float* __restrict__ weight, c
   if (t >= T) return;
   float* score = sm + (size_t)warp * 3 * NR;
   route_token_grouped(chosen, weight, logits + (size_t)t * NR, score, score + NR, score + 2 * NR, t, NR, top, renormalize,
-                      score_kind, groups, keep, wscale, lane);
+                      score_kind, groups, keep, wscale, lane, correction);
 }
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
@@ -245,7 +247,7 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
   if (warp == 0) {
     if (GROUPED)
       route_token_grouped(chosen, weight, z, z + NR, z + 2 * NR, z + 3 * NR, t, NR, top, renormalize, score_kind, groups, keep,
-                          wscale, lane);
+                          wscale, lane, correction);
     else
       route_token(chosen, weight, z, z + NR, z + 2 * NR, correction, t, NR, top, renormalize, lane);
   }
@@ -432,6 +434,12 @@ extern "C" int zi_moe_route(int* chosen, float* weight, const float* logits, con
 extern "C" int zi_moe_route_grouped(int* chosen, float* weight, const float* logits, int T, int NR, int top,
                                     int renormalize, int score_kind, int groups, int keep, float wscale,
                                     cudaStream_t stream) {
+  return zi_moe_route_grouped_c(chosen, weight, logits, nullptr, T, NR, top, renormalize, score_kind, groups, keep, wscale, stream);
+}
+
+extern "C" int zi_moe_route_grouped_c(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR,
+                                      int top, int renormalize, int score_kind, int groups, int keep, float wscale,
+                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= 0 || top > NR) return zi_refuse("moe_route: %d of %d outputs cannot be chosen", top, NR);
   if (groups <= 0 || NR % groups || keep <= 0 || keep > groups)
@@ -441,7 +449,7 @@ extern "C" int zi_moe_route_grouped(int* chosen, float* weight, const float* log
   const size_t smem = (size_t)ROUTE_WARPS * 3 * NR * sizeof(float);
   if (smem > 48 * 1024) return zi_refuse("moe_route: %d router outputs are more than this kernel holds", NR);
   zi_launch(moe_route_grouped_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen,
-            weight, logits, T, NR, top, renormalize, score_kind, groups, keep, wscale);
+            weight, logits, T, NR, top, renormalize, score_kind, groups, keep, wscale, correction);
   return zi_check_launch("moe_route_grouped");
 }
 
@@ -489,6 +497,13 @@ extern "C" int zi_moe_router_grouped(int* chosen, float* weight, const void* x, 
                                      int w_dtype, int T, int K, int NR, int top, int renormalize, int score_kind,
                                      int groups, int keep, float wscale, cudaStream_t stream) {
   return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, nullptr, T, K, NR, top, renormalize, true, score_kind,
+                           groups, keep, wscale, stream);
+}
+
+extern "C" int zi_moe_router_grouped_c(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w,
+                                       int w_dtype, const float* correction, int T, int K, int NR, int top, int renormalize,
+                                       int score_kind, int groups, int keep, float wscale, cudaStream_t stream) {
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, true, score_kind,
                            groups, keep, wscale, stream);
 }
 

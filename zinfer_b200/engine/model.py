@@ -16,6 +16,9 @@ from ..config.spec import ModelSpec
 from ..parts.base import BuildContext, KVCacheNeed, StateNeed, TensorSpec, make_part, prefixed, take
 
 
+EMBEDDING_STATE = "embedding"      # name of the state an embedding keeps per request (its last token)
+
+
 @dataclass(frozen=True)
 class Run:
     """One scheduled execution of a layer with the cache it uses."""
@@ -51,6 +54,7 @@ class DecoderModel:
         self.head = make_part(spec.head, self.ctx)
         self.runs = _plan_runs(spec)
         self._views: list = []
+        self._embedding_view = None
         self.tables: dict[str, torch.Tensor] = {}
 
     # ----------------------------------------------------------------- weights
@@ -99,10 +103,15 @@ class DecoderModel:
     # ------------------------------------------------------------------- caches
     def cache_needs(self) -> tuple[dict[str, KVCacheNeed], dict[str, StateNeed]]:
         kv, state = {}, {}
+        emb = self._embedding_need()
+        if emb is not None:
+            state[EMBEDDING_STATE] = emb
         for run in self.runs:
             for name, need in self._needs_of(run).items():
                 prev = kv.get(name, state.get(name))
-                if prev is not None and prev != need:
+                if isinstance(prev, KVCacheNeed) and isinstance(need, KVCacheNeed) and prev.same_pages(need):
+                    need = prev.merged(need)     # runs that share pages may look back differently far: keep the most
+                elif prev is not None and prev != need:
                     raise ValueError(f"cache {name!r} is shared by layers with different needs: {prev} and {need}")
                 if isinstance(need, KVCacheNeed):
                     kv[name] = need
@@ -111,6 +120,11 @@ class DecoderModel:
                 else:
                     raise TypeError(f"layer {run.layer}: unknown cache need {need!r}")
         return kv, state
+
+    def _embedding_need(self) -> Optional[StateNeed]:
+        """An embedding that looks at the token before keeps per-request state of its own."""
+        need = getattr(self.embedding, "cache_need", None)
+        return need() if need is not None else None
 
     def _needs_of(self, run: Run) -> dict:
         """The caches and states a run uses, by name.  A mixer needs one (named like the run's cache), none, or
@@ -132,6 +146,7 @@ class DecoderModel:
     def attach(self, storage: CacheStorage) -> None:
         """Binds every run to its view of the cache storage."""
         kv, state = self.cache_needs()
+        self._embedding_view = storage.state_view(EMBEDDING_STATE) if EMBEDDING_STATE in state else None
         self._views = []
         for run in self.runs:
             need = self.blocks[run.layer].mixer.cache_need()
@@ -145,7 +160,10 @@ class DecoderModel:
         """Runs the step's tokens through every scheduled layer (filling the caches)
         and returns 32-bit logits [wanted rows, vocab], or None if none are wanted.
         With ``argmax`` it returns the pair (logits, first maximum of every row as int32)."""
-        h = self.embedding.forward(step.token_ids)
+        if self._embedding_view is not None:
+            h = self.embedding.forward(step.token_ids, step, self._embedding_view)
+        else:
+            h = self.embedding.forward(step.token_ids)
         pending = None
         for run, view in zip(self.runs, self._views):
             if run.pre_add is None:

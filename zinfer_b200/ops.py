@@ -168,6 +168,76 @@ class Carried:
         self.x = x
 
 
+class Several:
+    """Updates of the residual stream that are still to be added, in this order (a block whose sublayers read the
+    same stream leaves one per sublayer): each a tensor, :class:`Partials`, or either inside :class:`Scaled`."""
+
+    def __init__(self, terms):
+        self.terms = [t for t in terms if t is not None]
+
+    @property
+    def shape(self):
+        return self.terms[0].shape
+
+
+def _terms_of(delta) -> list:
+    if delta is None or isinstance(delta, Carried):
+        return []
+    return list(delta.terms) if isinstance(delta, Several) else [delta]
+
+
+def sum_norm(h: torch.Tensor, delta, w1: torch.Tensor, eps: float, out_dtype: torch.dtype, w2: Optional[torch.Tensor] = None,
+             rows: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None):
+    """``h += `` every update of ``delta`` (a tensor, :class:`Partials`, :class:`Scaled`, or :class:`Several` of up to
+    four of them, added in order) and ``bias``, in place and in 32-bit; then the RMS norm of every row times ``w1`` and,
+    with ``w2``, the same norm times ``w2`` as well (two norms of one stream share their root mean square): one
+    kernel, one pass.  With ``rows`` the picked rows' norms are returned and ``h`` is left as it is.  Returns the norm,
+    or the pair of norms."""
+    T, H = h.shape
+    terms = _terms_of(delta)
+    _need(len(terms) <= 4, "at most four updates can be added at once")
+    _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
+    for w in (w1, w2):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == H), "norm weights are float32 of the row's width")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == H and bias.is_contiguous(), "the bias is float32 of the row's width")
+    n_terms = len(terms)
+    whole, part = (ctypes.c_void_p * 4)(), (ctypes.c_void_p * 4)()
+    dtypes, splits = (ctypes.c_int * 4)(), (ctypes.c_int * 4)()
+    zstride, scales = (ctypes.c_longlong * 4)(), (ctypes.c_float * 4)()
+    keep, nbytes = [], 0
+    for i, term in enumerate(terms):
+        t, scales[i] = _unscaled(term)
+        if isinstance(t, Partials):
+            _need(tuple(t.shape) == (T, H), "an update must match the residual stream")
+            part[i], splits[i], zstride[i] = t.data.data_ptr(), t.splits, T * H
+            keep.append(t.data)
+        else:
+            _need(tuple(t.shape) == (T, H) and t.is_contiguous(), "an update must match the residual stream")
+            whole[i], dtypes[i] = t.data_ptr(), _tag(t)
+            keep.append(t)
+        nbytes += _nb(keep[-1])
+    n = T if rows is None else _i32(rows, "rows").shape[0]
+    out1 = torch.empty((n, H), dtype=out_dtype, device=h.device)
+    out2 = torch.empty_like(out1) if w2 is not None else None
+    with _prof.region("sum of updates + norm" + (" pair" if w2 is not None else ""),
+                      lambda: (2 if rows is None else 1) * n * H * 4 + nbytes + _nb(out1) * (2 if w2 is not None else 1)):
+        _check(lib().zi_sum_norm_pair(_ptr(h), n_terms, whole, dtypes, part, splits, zstride, scales, _ptr(bias), _ptr(w1),
+                                      _ptr(w2), ctypes.c_float(eps), _ptr(out1), _ptr(out2), _tag(out1), _ptr(rows), n, H,
+                                      _stream()), "sum_norm")
+    return out1 if w2 is None else (out1, out2)
+
+
+def add_rmsnorm_pair(h: torch.Tensor, delta, w1: torch.Tensor, w2: torch.Tensor, eps1: float, eps2: float,
+                     out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None):
+    """Both norms of a block whose two sublayers read the same stream: ``h += delta`` (see :func:`sum_norm`), then
+    ``(norm(h) * w1, norm(h) * w2)``; one kernel when both norms have the same eps."""
+    if eps1 == eps2:
+        return sum_norm(h, delta, w1, eps1, out_dtype, w2=w2, bias=bias)
+    x1 = sum_norm(h, delta, w1, eps1, out_dtype, bias=bias)
+    return x1, sum_norm(h, None, w2, eps2, out_dtype)
+
+
 def _unscaled(delta):
     """(update, multiplier) of an update given plain or as :class:`Scaled`; nothing for :class:`Carried`."""
     if isinstance(delta, Carried):
@@ -191,6 +261,31 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
+def embed_bigram(table: torch.Tensor, bigram: Optional[torch.Tensor], ids: torch.Tensor, step, last_token: torch.Tensor,
+                 scale: float, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """The 32-bit residual stream ``scale * table[ids] + bigram[row]``: ``row`` is ``(previous token * mul_prev + token *
+    mul_cur) mod buckets``, or ``buckets`` (the table's last row) for a request's first token.  The token before a
+    portion's first token is ``last_token[slot]`` (int32 [slots, 1], one per request), which then receives the portion's
+    last token.  ``bigram`` None: the scaled rows alone."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _need(table.is_contiguous(), "embedding table must be contiguous")
+    if bigram is not None:
+        _need(bigram.is_contiguous() and bigram.dtype == table.dtype and tuple(bigram.shape) == (buckets + 1, H),
+              "the pair table has one row per bucket and one more, in the embedding's type")
+    _need(last_token.dtype == torch.int32 and last_token.is_contiguous() and last_token[0].numel() == 1,
+          "the last tokens are int32, one per request slot")
+    for t, name in ((ids, "ids"), (step.positions, "positions"), (step.cu_q, "cu_q"), (step.state_slots, "state_slots")):
+        _i32(t, name)
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    with _prof.region("embed (scaled, with a table of token pairs)", lambda: 2 * T * H * table.element_size() + _nb(out, ids)):
+        _check(lib().zi_embed_bigram(_ptr(out), _ptr(table), _ptr(bigram), _tag(table), _ptr(ids), _ptr(step.positions),
+                                     _ptr(step.cu_q), _ptr(step.state_slots), _ptr(last_token), step.n_seqs, T, H, V,
+                                     ctypes.c_float(scale), int(buckets), ctypes.c_longlong(int(mul_prev)),
+                                     ctypes.c_longlong(int(mul_cur)), _stream()), "embed_bigram")
+    return out
+
+
 def patch_tokens(ids: torch.Tensor, prev: torch.Tensor, dst: torch.Tensor, src: torch.Tensor) -> None:
     """``ids[dst[i]] = prev[src[i]]`` where ``dst[i] >= 0``: feeds tokens sampled by the
     step before without a round trip through the host."""
@@ -209,6 +304,9 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     ``rows`` (int32, repeats allowed) picks rows instead: the result has one row per entry,
     the norm of ``h[row] + delta[row]``, and ``h`` is left unchanged."""
     T, H = h.shape
+    if isinstance(delta, Several):      # several updates at once: the kernel that adds them all in one pass
+        _need(out is None, "several updates at once come with a new output tensor")
+        return sum_norm(h, delta, weight, eps, out_dtype, rows=rows, bias=bias)
     delta, dscale = _unscaled(delta)
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == H and bias.is_contiguous(), "the bias is float32 of the row's width")
@@ -233,6 +331,10 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float,
 
 
 def residual_add(h: torch.Tensor, delta) -> None:
+    if isinstance(delta, Several):
+        for term in delta.terms:
+            residual_add(h, term)
+        return
     delta, dscale = _unscaled(delta)
     if isinstance(delta, Partials):
         delta = delta.sum(torch.float32)
@@ -343,13 +445,15 @@ def qk_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: i
                q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
-               page_size: int, values_from_keys: bool = False, write_kv: bool = True) -> torch.Tensor:
+               page_size: int, values_from_keys: bool = False, write_kv: bool = True,
+               value_dim: Optional[int] = None) -> torch.Tensor:
     """The general form of :func:`qk_norm_rope_store`: the rotation turns only the first ``rot_dims`` dimensions of a
     head (pairs (i, i + rot_dims/2), tables [positions, rot_dims/2]), and with ``values_from_keys`` the rows are
     [q heads | k heads] and a token's value is its key AS PROJECTED, before norm and rotation.  Rewrites q in place
-    and returns ``qkv``."""
+    and returns ``qkv``.  ``value_dim``: the size of a value head where it differs from ``head_dim``."""
     T = qkv.shape[0]
-    width = (num_heads + ((1 if values_from_keys else 2) * num_kv_heads if write_kv else 0)) * head_dim
+    dv = int(value_dim or head_dim)
+    width = num_heads * head_dim + ((num_kv_heads * head_dim + (0 if values_from_keys else num_kv_heads * dv)) if write_kv else 0)
     _need(qkv.stride(1) == 1 and qkv.shape[1] >= width, "qk_prepare: dense rows as wide as their heads")
     for wt in (q_weight, k_weight):
         if wt is not None:
@@ -365,8 +469,8 @@ def qk_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: i
         _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache pages have the activations' dtype")
         _i32(slots, "slots")
     with _prof.region("qk_prepare (norm, partial rotation, page write)", lambda: 2 * T * width * qkv.element_size()):
-        _check(lib().zi_qk_prepare(_ptr(qkv), _tag(qkv), T, qkv.stride(0), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads,
-                                   head_dim, rot_dims, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+        _check(lib().zi_qk_prepare_v(_ptr(qkv), _tag(qkv), T, qkv.stride(0), _ptr(qkv), qkv.stride(0), num_heads, num_kv_heads,
+                                   head_dim, dv, rot_dims, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
                                    n_table, _ptr(positions), _ptr(k_cache), _ptr(v_cache), _ptr(slots), page_size,
                                    1 if values_from_keys else 0, 1 if write_kv else 0, _stream()), "qk_prepare")
     return qkv
@@ -936,9 +1040,12 @@ def attention_tile_rows() -> int:
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                     cu_q: torch.Tensor, kv_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                    scale: float, out: Optional[torch.Tensor] = None, sink: float = 0.0) -> torch.Tensor:
+                    scale: float, out: Optional[torch.Tensor] = None, sink: float = 0.0, keep_first: int = 0,
+                    value_dim: Optional[int] = None) -> torch.Tensor:
     """Causal attention of the step's query tokens over their requests' pages.  ``sink``: that many keys of
     score 0 without a value are counted in the softmax's denominator (p_j = exp(s_j) / (sink + sum exp(s))).
+    ``keep_first``: with a window, a request's first tokens that stay visible beyond it (query i sees key j <= i if
+    i - j < window or j < keep_first).  ``value_dim``: the values' size where it differs from the keys'.
 
     ``q`` [T, >= num_heads*head_dim] (row stride free), caches [pages, kv heads,
     page_size, head_dim], ``block_tables`` [n, W], ``cu_q`` [n+1] token offsets,
@@ -949,17 +1056,20 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache pages must be contiguous")
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim), "cache pages are [pages, kv heads, page, d]")
     _need(k_cache.dtype == q.dtype, "cache pages have the activations' dtype")
+    dv = int(value_dim or head_dim)
+    _need(tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, dv) and v_cache.dtype == q.dtype,
+          "value pages are [pages, kv heads, page, value size]")
     for name, t in (("block_tables", block_tables), ("cu_q", cu_q), ("kv_lens", kv_lens), ("tile_seq", tile_seq),
                     ("tile_q0", tile_q0)):
         _i32(t, name)
     if out is None:
-        out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, num_heads * dv), dtype=q.dtype, device=q.device)
     with _prof.region("attention (exact, CUDA cores)"):
-        _check(lib().zi_paged_attention_sink(
+        _check(lib().zi_paged_attention_mask(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
             block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
-            num_heads, num_kv_heads, head_dim, head_dim, head_dim, page_size, int(window or 0), ctypes.c_float(scale),
-            0, 0, ctypes.c_float(sink), _stream()), "paged_attention")
+            num_heads, num_kv_heads, head_dim, dv, dv, page_size, int(window or 0), int(keep_first or 0),
+            ctypes.c_float(scale), 0, 0, ctypes.c_float(sink), _stream()), "paged_attention")
     return out
 
 
@@ -989,7 +1099,7 @@ def attention_prefill_tile_rows() -> int:
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, step,
               num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-              scale: float, sink: float = 0.0) -> torch.Tensor:
+              scale: float, sink: float = 0.0, keep_first: int = 0, value_dim: Optional[int] = None) -> torch.Tensor:
     """Attention of a step's query tokens over their pages, by the fastest kernel that
     takes the shape: in bfloat16 with head sizes 64/128 (decode also 256) the
     tensor-core kernels (requests that bring one token go to the split-key decode
@@ -997,13 +1107,17 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     exact CUDA-core kernel.  ``step`` is the StepContext (its request arrays)."""
     T = q.shape[0]
     L = lib()
-    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16
+    keep_first = int(keep_first or 0) if window else 0
+    same_size = value_dim is None or int(value_dim) == head_dim
+    # the tensor-core kernels take values of the keys' size and no kept first tokens
+    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and not keep_first
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
         return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-                               num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink)
+                               num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink,
+                               keep_first=keep_first, value_dim=value_dim)
     _need(q.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: dense operands")
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.dtype == q.dtype,
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
@@ -1342,9 +1456,13 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torc
 
 
 def moe_router_grouped(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", groups: int = 1, keep: int = 1,
-                       scale: float = 1.0, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+                       scale: float = 1.0, renormalize: bool = False,
+                       correction: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
     """The router's product (32-bit multiply-adds whatever the operands' types) and :func:`moe_route_grouped` in one
     kernel, one block per token."""
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.numel() == w_router.shape[0] and correction.is_contiguous(),
+              "the correction is float32, one value per router output")
     T, K = x.shape
     NR = w_router.shape[0]
     _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == K, "moe_router: shapes")
@@ -1352,26 +1470,31 @@ def moe_router_grouped(x: torch.Tensor, w_router: torch.Tensor, top: int, score:
     chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
     with _prof.region(f"moe router (groups) N={NR} K={K}", lambda: _nb(w_router) + T * K * x.element_size(), 2 * T * NR * K):
-        _check(lib().zi_moe_router_grouped(_ptr(chosen), _ptr(weight), _ptr(x), _tag(x), x.stride(0), _ptr(w_router),
-                                           _tag(w_router), T, K, NR, top, 1 if renormalize else 0,
+        _check(lib().zi_moe_router_grouped_c(_ptr(chosen), _ptr(weight), _ptr(x), _tag(x), x.stride(0), _ptr(w_router),
+                                           _tag(w_router), _ptr(correction), T, K, NR, top, 1 if renormalize else 0,
                                            1 if score == "sigmoid" else 0, groups, keep, ctypes.c_float(scale), _stream()),
                "moe_router_grouped")
     return chosen, weight
 
 
 def moe_route_grouped(logits: torch.Tensor, top: int, score: str = "sigmoid", groups: int = 1, keep: int = 1,
-                      scale: float = 1.0, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+                      scale: float = 1.0, renormalize: bool = False,
+                      correction: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
     """Per token: scores ``sigmoid(z)`` or ``softmax(z)``; the outputs form ``groups`` equal groups of neighbours, a
     group's score is the sum of its two largest scores, and the ``top`` largest scores are chosen among the outputs of
     the ``keep`` best groups (int32 [T, top]); their weights are the scores times ``scale`` (float32 [T, top]),
-    divided by the chosen scores' sum first if ``renormalize``."""
+    divided by the chosen scores' sum first if ``renormalize``.  ``correction`` (float32 [outputs]) is added to the scores
+    wherever they are compared, never to the weights."""
     T, NR = logits.shape
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.numel() == NR and correction.is_contiguous(),
+              "the correction is float32, one value per router output")
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "router logits are contiguous float32")
     _need(score in ("softmax", "sigmoid"), f"unknown router score {score!r}")
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     with _prof.region("moe route (groups)", lambda: _nb(logits, chosen, weight)):
-        _check(lib().zi_moe_route_grouped(_ptr(chosen), _ptr(weight), _ptr(logits), T, NR, top, 1 if renormalize else 0,
+        _check(lib().zi_moe_route_grouped_c(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(correction), T, NR, top, 1 if renormalize else 0,
                                           1 if score == "sigmoid" else 0, groups, keep, ctypes.c_float(scale), _stream()),
                "moe_route_grouped")
     return chosen, weight

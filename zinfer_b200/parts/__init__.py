@@ -1,8 +1,8 @@
 from .base import (Block, BuildContext, FeedForward, KVCacheNeed, Mixer, Norm, Part, PositionEncoding, StateNeed,
                    TensorSpec, make_part, prefixed, register_part, take, unregister_part)
 from .attention import GQAttention
-from .block import OutputNormBlock, PreNormBlock
-from .embedding import LMHead, TokenEmbedding
+from .block import OutputNormBlock, ParallelBlock, PreNormBlock
+from .embedding import HashedBigramEmbedding, LMHead, TokenEmbedding
 from .latent_attention import LatentAttention
 from .linear_attention import GatedDeltaRule, GatedLinearAttention, ParallelMixer
 from .mlp import PlainMLP, SwiGLUMLP
@@ -16,11 +16,13 @@ for _kind, _cls in (("rmsnorm", RMSNorm), ("rope", RotaryPosition), ("no_positio
                     ("token_embedding", TokenEmbedding), ("lm_head", LMHead), ("latent_attention", LatentAttention),
                     ("rglru", RGLRUMixer), ("routed_experts", RoutedExperts), ("outnorm_block", OutputNormBlock),
                     ("plain_mlp", PlainMLP), ("gated_linear_attention", GatedLinearAttention),
-                    ("gated_delta_rule", GatedDeltaRule), ("parallel_mixer", ParallelMixer)):
+                    ("gated_delta_rule", GatedDeltaRule), ("parallel_mixer", ParallelMixer),
+                    ("parallel_block", ParallelBlock), ("hashed_bigram_embedding", HashedBigramEmbedding)):
     register_part(_kind, _cls, replace=True)
 
 __all__ = [
-    "Block", "BuildContext", "FeedForward", "GQAttention", "GatedDeltaRule", "GatedLinearAttention", "OutputNormBlock",
+    "Block", "BuildContext", "FeedForward", "GQAttention", "GatedDeltaRule", "GatedLinearAttention", "HashedBigramEmbedding",
+    "OutputNormBlock", "ParallelBlock",
     "ParallelMixer", "PlainMLP", "KVCacheNeed", "LMHead", "LatentAttention", "Mixer",
     "NoPosition", "Norm", "Part", "PositionEncoding", "PreNormBlock", "RGLRUMixer", "RMSNorm", "RotaryPosition",
     "RoutedExperts", "StateNeed", "SwiGLUMLP", "TensorSpec",

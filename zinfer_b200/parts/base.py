@@ -64,12 +64,29 @@ class KVCacheNeed:
     """Keys and values per token in pages.  ``window`` None: every earlier key stays
     visible; an integer w: a query at position i reads keys i-w+1 .. i, and pages
     wholly behind that may be given back.  ``values`` False: the pages hold keys only (a mixer
-    whose values are part of its key rows, such as a latent shared by keys and values)."""
+    whose values are part of its key rows, such as a latent shared by keys and values).
+    ``value_dim``: the size of a value when it differs from a key's (None: ``head_dim``).  ``keep_first``:
+    with a window, the request's first tokens that stay visible to every later query, so that the pages
+    which hold them are never given back.  Runs that share a cache may want different windows; the cache
+    then keeps what the most demanding of them reads (:meth:`merged`)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    value_dim: Optional[int] = None
+    keep_first: int = 0
+
+    def same_pages(self, other: "KVCacheNeed") -> bool:
+        """Whether both describe pages of the same layout (whatever they keep of them)."""
+        return (self.num_kv_heads, self.head_dim, self.values, self.value_dim or self.head_dim) == \
+            (other.num_kv_heads, other.head_dim, other.values, other.value_dim or other.head_dim)
+
+    def merged(self, other: "KVCacheNeed") -> "KVCacheNeed":
+        """The need of a cache that serves both: the wider window (none if either has none), the longer kept start."""
+        window = None if self.window is None or other.window is None else max(self.window, other.window)
+        keep = 0 if window is None else max(self.keep_first, other.keep_first)
+        return KVCacheNeed(self.num_kv_heads, self.head_dim, window, self.values, self.value_dim, keep)
 
 
 @dataclass(frozen=True)

@@ -90,3 +90,23 @@ class OutputNormBlock(PreNormBlock):
         a, b = out if isinstance(out, tuple) else (out, None)              # routed experts beside a shared one
         x = ops.norm_residual(h, a, self.ffn_norm.weight, self.ffn_norm.eps, self.ctx.dtype, b=b)
         return ops.Carried(x)
+
+
+class ParallelBlock(PreNormBlock):
+    """The arrangement whose two sublayers read the SAME stream: h1 = h + mixer(norm1(h)) + ffn(norm2(h)), each norm
+    with its own weight.  Same parameters and tensor names as :class:`PreNormBlock`.
+
+    Both norms share their root mean square, so one kernel makes both from one pass over the stream, and the same
+    pass adds what the block before left pending.  The block leaves all its updates pending as :class:`ops.Several`
+    (the mixer's output, the feed-forward's, and a shared expert's where the feed-forward hands back a pair): the
+    next block's norm, or the model's last one, adds them, in this order."""
+
+    def forward(self, h, pending, step, cache, bias=None):
+        if self.feed_forward is None:
+            x = ops.sum_norm(h, pending, self.mixer_norm.weight, self.mixer_norm.eps, self.ctx.dtype, bias=bias)
+            return self._update(self.mixer.forward(x, step, cache))
+        x1, x2 = ops.add_rmsnorm_pair(h, pending, self.mixer_norm.weight, self.ffn_norm.weight, self.mixer_norm.eps,
+                                      self.ffn_norm.eps, self.ctx.dtype, bias=bias)
+        a = self.mixer.forward(x1, step, cache)
+        out = self.feed_forward.forward(x2)
+        return ops.Several([self._update(t) for t in (a, *(out if isinstance(out, tuple) else (out,)))])

@@ -1,14 +1,14 @@
 """Mixture of experts: every token runs ``top`` of ``experts`` small feed-forwards and takes the
 weighted sum of their outputs.
 
-Router: logits z = W_r h over ``experts + identity`` outputs in 32-bit, scores s = softmax(z)
-(``sigmoid`` is not built).  A token chooses the ``top`` outputs with the largest s + correction
+Router: logits z = W_r h over ``experts + identity`` outputs in 32-bit, scores s = softmax(z).  A token chooses the ``top`` outputs with the largest s + correction
 (a per-output vector; the selection bias of auxiliary-loss-free balancing) and weights them by
 s without the correction, divided by their sum only if ``renormalize``.  The last ``identity``
 outputs stand for experts without weights whose output is their input.  An expert is
 W_down act(W_up h) with act the square of relu (``relu2``).
 
 Other routers and experts, by parameter: ``score: sigmoid`` scores each output alone, s = sigmoid(z);
+a ``correction`` is then added to the sigmoid scores for the choice alone, as with the softmax;
 ``groups`` / ``groups_kept`` cut the experts into equal groups of neighbours, score a group by the sum of its two
 largest scores and let only experts of the best groups be chosen; ``weight_scale`` multiplies the weights;
 ``activation: silu_gated`` makes an expert W_down (silu(W_gate h) * (W_up h)); ``shared`` (a feed-forward part) runs
@@ -49,8 +49,8 @@ class RoutedExperts(FeedForward):
         # the fused router kernel has the softmax over all outputs; everything else takes the general choice
         self.general_route = self.score != "softmax" or self.groups > 1 or self.weight_scale != 1.0
         if self.general_route:
-            if self.identity or self.has_correction:
-                raise ValueError("identity experts and a correction are built for the softmax router without groups only")
+            if self.identity:
+                raise ValueError("identity experts are built for the softmax router without groups only")
             if self.groups <= 0 or self.experts % self.groups or not 1 <= self.groups_kept <= self.groups:
                 raise ValueError(f"{self.experts} experts do not form {self.groups} groups of which {self.groups_kept} are kept")
             if self.top > self.groups_kept * (self.experts // self.groups):
@@ -115,11 +115,11 @@ class RoutedExperts(FeedForward):
         relu2 = not self.gated
         if self.general_route and self.hidden <= 32768:
             chosen, weight = ops.moe_router_grouped(x, self.w_router, self.top, self.score, self.groups, self.groups_kept,
-                                                    self.weight_scale, self.renormalize)
+                                                    self.weight_scale, self.renormalize, correction=self.correction)
         elif self.general_route:
             logits = ops.linear_cuda_cores(x, self.w_router, out_dtype=torch.float32)     # 32-bit multiply-adds
             chosen, weight = ops.moe_route_grouped(logits, self.top, self.score, self.groups, self.groups_kept,
-                                                   self.weight_scale, self.renormalize)
+                                                   self.weight_scale, self.renormalize, correction=self.correction)
         elif self.hidden <= 32768:      # the router's product and the choice in one kernel (the row fits its shared memory)
             chosen, weight = ops.moe_router(x, self.w_router, self.correction, self.top, self.renormalize)
         else:
