@@ -23,7 +23,8 @@ With ``--design luvavik`` it runs another measurement instead and prints a JSON 
 (2,048 tokens) and decode (batch 8, 2,048 cached tokens each) throughput of the Luvavik design at layer
 sizes of real models (widths 2048 and 4096; ``--design-sizes``), beside Qwen3 dense at the same width,
 layer count and multiply-adds per token; ``--design rogosun`` does the same for the Rogosun design, beside
-Luvavik (the nearest design the engine has) and Qwen3; ``--profile PATH`` adds both models' per-kernel-class times and
+Luvavik (the nearest design the engine has) and Qwen3, and ``--design vumezen`` for the Vumezen design, beside
+Rogosun (whose attention with a sink and routed experts beside a shared one are the nearest the engine has) and Qwen3; ``--profile PATH`` adds both models' per-kernel-class times and
 roofline fractions.  The default workload and its output line are untouched.
 
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback
@@ -163,6 +164,26 @@ def rogosun_shape(width: int, heads: int, experts: int, top: int, expert_ff: int
             "max_position_embeddings": 8192}
 
 
+def vumezen_shape(width: int, heads: int, experts: int, top: int, expert_ff: int, dense_ff: int) -> dict:
+    """A Vumezen configuration with layers the size of a real model's: blocks whose two sublayers read the same
+    stream; attention heads of 128 of which 64 dimensions rotate, four query heads per kv head, values of 128, a
+    sink, a window of 1,024 tokens that keeps a request's first four; every second layer reads the keys and values
+    of the layer before it; relu-squared experts chosen by sigmoid scores beside a shared expert in every layer; a
+    table of token pairs beside the embedding.  Seven layers."""
+    def mixer(src=None):
+        m = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+             "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": 1024, "keep_first": 4}}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.0}}
+    layers = [{"type": "attention", "mixer": mixer(i - 1 if i % 2 else None), "mlp": moe} for i in range(7)]
+    return {"architecture": "Vumezen", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "max_position_embeddings": 8192}
+
+
 DESIGN_SIZES = {
     # name: (width, heads, experts, chosen, expert ff, dense ff); Qwen3 beside it: the same width, layer runs and
     # heads of 128, a feed-forward as wide as the chosen experts together (equal products per token)
@@ -247,7 +268,16 @@ def compare_designs(args) -> int:
             from zinfer_b200.config import RogosunConfig
             own = rogosun_shape(width, heads, experts, top, eff, dff)
             results[f"rogosun_{size}"] = measure(f"rogosun_{size}", RogosunConfig.from_dict(own), own["vocab"])
-        results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
+        if args.design == "vumezen":
+            # beside Rogosun, whose attention (a sink, the same tensor-core kernels) and experts (sigmoid scores, a shared
+            # expert) are the nearest the engine has, and Qwen3
+            from zinfer_b200.config import RogosunConfig, VumezenConfig
+            own = vumezen_shape(width, heads, experts, top, eff, dff)
+            results[f"vumezen_{size}"] = measure(f"vumezen_{size}", VumezenConfig.from_dict(own), own["vocab"])
+            other = rogosun_shape(width, heads, experts, top, eff, dff)
+            results[f"rogosun_{size}"] = measure(f"rogosun_{size}", RogosunConfig.from_dict(other), other["vocab"])
+        else:
+            results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
         # two products of an expert against three of the gated feed-forward: equal multiply-adds per token
         qwen = dict(QWEN3_8B, vocab_size=raw["vocab"], hidden_size=width, intermediate_size=(2 * top * eff) // 3 // 64 * 64,
                     num_hidden_layers=7, num_attention_heads=heads, num_key_value_heads=max(1, heads // 4), head_dim=128,
@@ -256,7 +286,8 @@ def compare_designs(args) -> int:
     if args.profile:
         with open(args.profile, "w") as f:
             json.dump(profiles, f, indent=1)
-    names = "Rogosun beside Luvavik and Qwen3 dense" if args.design == "rogosun" else "Luvavik beside Qwen3 dense"
+    names = {"rogosun": "Rogosun beside Luvavik and Qwen3 dense", "vumezen": "Vumezen beside Rogosun and Qwen3 dense"}.get(
+        args.design, "Luvavik beside Qwen3 dense")
     print(json.dumps({"metric": f"prefill and decode tokens/s, {names} at equal width and layer runs",
                       "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
                       "data": "synthetic", "config": {"prefill_tokens": tokens, "decode_batch": batch, "context": context,
@@ -280,7 +311,7 @@ def main() -> int:
                     help="with ZINFER_B200_TRACE=1 in the environment: write the timeline of one decode step at the "
                          "headline batch (every kernel's start, the completion of what it depends on, and what it adds "
                          "to the chain) there as JSON, and do nothing else")
-    ap.add_argument("--design", default=None, choices=["luvavik", "rogosun"],
+    ap.add_argument("--design", default=None, choices=["luvavik", "rogosun", "vumezen"],
                     help="instead of the default benchmark: prefill and decode throughput of this design at layer sizes "
                          "of real models beside Qwen3 dense at equal size (a JSON line of its own)")
     ap.add_argument("--design-sizes", default=None, help="with --design: widths to run, e.g. 2048 or 2048,4096")

@@ -561,7 +561,7 @@ def qk_prepare(qkv, num_heads, num_kv_heads, head_dim, rot_dims, q_weight, k_wei
                 continue
             k_cache[slot // page_size, :, slot % page_size] = kn[t].to(k_cache.dtype)
             v_cache[slot // page_size, :, slot % page_size] = v[t].to(v_cache.dtype)
-    qkv[:, :nq * d] = qn.reshape(T, nq * d).to(qkv.dtype)
+    qkv[:, :nq * d] = qn.reshape(T, nq * d).to(qkv.dtype).clone()      # (qn is qkv itself where nothing was done to it)
     return qkv
 
 

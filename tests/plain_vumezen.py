@@ -54,12 +54,20 @@ def embed(tokens, prev, w, e):
 # ----------------------------------------------------------------------------------- attention
 def rotate(x, positions, dims, base):
     """x [T, heads, d]: the first ``dims`` dimensions in pairs (i, i + dims/2); angle position * base^(-2i/dims)."""
+    if not dims:
+        return x
     half = dims // 2
     f = torch.tensor([float(base) ** (-2.0 * i / dims) for i in range(half)], dtype=F64)
     a = positions.to(F64).unsqueeze(-1) * f
     c, s = torch.cos(a).unsqueeze(1), torch.sin(a).unsqueeze(1)
     u, v = x[..., :half], x[..., half:dims]
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
+
+
+def _rot(m):
+    """(dims, base) of a mixer's rotation; a mixer whose configuration names none does not rotate."""
+    rot = m.get("rot")
+    return (0, 1.0) if rot is None else (int(rot["dims"]), float(rot["base"]))
 
 
 def visible(i, j, size, keep_first):
@@ -71,7 +79,7 @@ def project_kv(h, p, m, pos0):
     T = h.shape[0]
     G, D, V = m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
     pos = torch.arange(pos0, pos0 + T)
-    k = rotate((h @ _w(p["k"]).T).view(T, G, D), pos, m["rot"]["dims"], m["rot"]["base"])
+    k = rotate((h @ _w(p["k"]).T).view(T, G, D), pos, *_rot(m))
     v = (h @ _w(p["v"]).T).view(T, G, V)
     return k, v
 
@@ -81,9 +89,10 @@ def attend(h, p, m, pos0, keys, values):
     hold every position from 0 up to the last of these tokens."""
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
-    size, keep = m["mask"]["size"], m["mask"].get("keep_first", 0)
+    mask = m.get("mask") or {"size": 1 << 60}          # no mask named: plain causal attention
+    size, keep = mask["size"], mask.get("keep_first", 0)
     pos = torch.arange(pos0, pos0 + T)
-    q = rotate((h @ _w(p["q"]).T).view(T, H, D), pos, m["rot"]["dims"], m["rot"]["base"])
+    q = rotate((h @ _w(p["q"]).T).view(T, H, D), pos, *_rot(m))
     out = torch.zeros(T, H, V, dtype=F64)
     for t in range(T):
         i = pos0 + t

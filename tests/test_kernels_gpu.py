@@ -468,6 +468,44 @@ def test_attention_with_a_sink_on_the_tensor_cores(nq, nkv, d, page, window):
     o.require_kernel_status_ok("attention with a sink")
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window,keep", [(8, 2, 64, 16, 37, 3), (3, 1, 128, 8, 100, 70), (4, 4, 64, 32, 64, 64),
+                                                        (16, 2, 128, 16, 1, 1), (5, 1, 64, 16, 200, 130), (2, 1, 256, 16, 50, 7),
+                                                        (4, 2, 64, 16, 30, 0)])
+def test_window_that_keeps_first_tokens_on_the_tensor_cores(nq, nkv, d, page, window, keep):
+    """A window that keeps a request's first tokens visible, with a sink, by the tensor-core kernels: the kept keys'
+    tiles are walked before the window's (and shared among the key splits).  Kept tokens fewer than a tile, more than
+    a tile, as many as the window; contexts that end inside the kept tokens, between them and the window's start, and
+    far behind; against the reference, whose answer must move when the kept tokens are taken away."""
+    o = ops()
+    for q_lens, ctx_lens in (([1] * 10, [0, 2, keep, window - 1, window, window + keep, 63, 191, 700, 1300]),
+                             ([1, 130, 17, 1, 300, 2], [5, 0, 250, 1000, 40, window + keep])):
+        args = _paged_case(torch.bfloat16, nq, nkv, d, page, q_lens, ctx_lens, seed=26)
+        step = _as_step(args, q_lens, ctx_lens)
+        scale = float(0.5 / np.sqrt(d))
+        want = ref.paged_attention(window=window, scale=scale, sink=1.0, keep_first=keep, **args).float()
+        if keep:
+            lost = ref.paged_attention(window=window, scale=scale, sink=1.0, **args).float()
+            assert (want - lost).abs().max() > 0.05 * want.abs().max()                 # the kept tokens matter
+        exact = o.paged_attention(window=window, scale=scale, sink=1.0, keep_first=keep, **args).float()
+        torch.testing.assert_close(exact, want, rtol=1.6e-2, atol=1.5e-2)
+        if d == 256 and max(q_lens) > 1:
+            continue                                  # prompt portions of heads of 256 go to the exact kernel
+        try:
+            for tma in (True, False):
+                o.decode_tma(tma)
+                for on in (True, False):
+                    o.decode_transposed_tile(on)
+                    for forced in (1, 3, 32):
+                        step.max_kv_len = 64 * forced
+                        got = o.attention(args["q"], args["k_cache"], args["v_cache"], args["block_tables"], step, nq, nkv, d,
+                                          page, window, scale, sink=1.0, keep_first=keep).float()
+                        torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.5e-2)
+        finally:
+            o.decode_transposed_tile(True)
+            o.decode_tma(1)
+    o.require_kernel_status_ok("attention with kept first tokens")
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window,norm,rope,partial", [
     (32, 8, 128, 16, None, True, True, True), (8, 2, 128, 16, None, True, True, False), (6, 1, 64, 8, 50, True, True, False),
     (5, 5, 64, 32, None, False, True, False), (16, 1, 128, 16, None, True, False, False), (2, 1, 256, 16, None, True, True, False)])

@@ -234,6 +234,17 @@ int zi_attention_decode_mma_sink(void* out, int out_stride, float* workspace, co
                                  int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq,
                                  int nkv, int d, int page_size, int window, float scale, int splits, float sink,
                                  cudaStream_t stream);
+// The two kernels with a sink and a window that keeps a request's first keep_first tokens visible.
+int zi_attention_prefill_mma_mask(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                  const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                  const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                                  int d, int page_size, int window, int keep_first, float scale, float sink,
+                                  cudaStream_t stream);
+int zi_attention_decode_mma_mask(void* out, int out_stride, float* workspace, const void* q, int q_stride, const void* kcache,
+                                 const void* vcache, long long n_pages, const int* block_tables, int bt_stride,
+                                 const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
+                                 int page_size, int window, int keep_first, float scale, int splits, float sink,
+                                 cudaStream_t stream);
 long long zi_attention_decode_workspace_floats(int n_dec, int nq, int nkv, int d, int splits);
 int zi_attention_decode_mma(void* out, int out_stride, float* workspace, const void* q, int q_stride,
                             const void* kcache, const void* vcache, long long n_pages, const int* block_tables, int bt_stride,

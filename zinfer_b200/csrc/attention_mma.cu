@@ -29,6 +29,8 @@ constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
 
 // XP: the softmax weights meet the values as two bfloat16 parts (high and rest: 16 bits of mantissa), and `sink`
 // keys of score 0 without a value count in the denominator.
+// With a window, a request's first keep_first keys stay visible (query i sees key j <= i if i - j < window or
+// j < keep_first): the tiles of those keys that lie before the window's first tile are walked first.
 template <int D, bool XP>
 __global__ void __launch_bounds__(PF_THREADS, 2)
 attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
@@ -36,7 +38,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
                         const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int page_shift,
-                        int window, float scale_log2, float sink) {
+                        int window, float scale_log2, float sink, int keep_first) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
@@ -65,7 +67,11 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
     cp_async16(qs + swz<D>(r, c), src, valid);
   }
   const int kt0 = (kv_lo / PF_BK) * PF_BK;
-  const int n_tiles = (kv_hi - kt0 + PF_BK - 1) / PF_BK;
+  // (only in the form with a sink; the plain form's code stays as it was: everything below folds away)
+  const int keep_end = XP && window > 0 ? min(keep_first, kv_lo) : 0;      // keys [0, keep_end) lie before the window and stay visible
+  const int n_keep = (min(keep_end, kt0) + PF_BK - 1) / PF_BK;       // their tiles before the window's first tile
+  const int n_tiles = n_keep + (kv_hi - kt0 + PF_BK - 1) / PF_BK;
+  auto tile_kt = [&](int t) { return t < n_keep ? t * PF_BK : kt0 + (t - n_keep) * PF_BK; };
 
   // Each thread copies NPER 16-byte chunks of K and of V per tile: rows r_i = tid / CH +
   // i * (256 / CH), column c = tid % CH.  The pages of its rows are looked up one tile
@@ -77,7 +83,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
       const int j = kt + my_r + i * RSTEP;
-      pg[i] = (j >= kv_lo && j < kv_hi) ? __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size))) : -1;
+      pg[i] = ((j >= kv_lo || j < keep_end) && j < kv_hi) ? __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size))) : -1;
     }
   };
   auto issue = [&](int kt, int buf) {
@@ -92,10 +98,10 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
       cp_async16(vbuf + buf * TILE_BYTES + so, vcache + off, valid);
     }
   };
-  lookup(kt0);
-  issue(kt0, 0);
+  lookup(tile_kt(0));
+  issue(tile_kt(0), 0);
   cp_async_commit();
-  if (n_tiles > 1) lookup(kt0 + PF_BK);
+  if (n_tiles > 1) lookup(tile_kt(1));
 
   float o[D / 8][4];
 #pragma unroll
@@ -107,20 +113,21 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
   const uint32_t qs_addr = smem_addr(qs);
 
   for (int t = 0; t < n_tiles; ++t) {
-    const int kt = kt0 + t * PF_BK;
+    const int kt = tile_kt(t);
     const int buf = t & 1;
     if (t + 1 < n_tiles) {
-      issue(kt + PF_BK, buf ^ 1);
+      issue(tile_kt(t + 1), buf ^ 1);
       cp_async_commit();
-      if (t + 2 < n_tiles) lookup(kt + 2 * PF_BK);
+      if (t + 2 < n_tiles) lookup(tile_kt(t + 2));
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    // a warp whose rows all lie before this tile (causal) or after it (window) has nothing to do
+    // a warp whose rows all lie before this tile (causal) or after it (window, unless the tile holds kept first
+    // keys: those of the window's own first tiles count too, for the block's later rows) has nothing to do
     const bool tile_visible = warp_active && kt <= warp_last_pos &&
-                              (window <= 0 || kt + PF_BK - 1 > warp_first_pos - window);
+                              (window <= 0 || kt + PF_BK - 1 > warp_first_pos - window || (XP && kt < keep_first));
     if (tile_visible) {
       const uint32_t ks_addr = smem_addr(kbuf + buf * TILE_BYTES), vs_addr = smem_addr(vbuf + buf * TILE_BYTES);
       float s[PF_BK / 8][4];
@@ -150,7 +157,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
           if (need_mask) {
             const int j = kt + nt * 8 + 2 * (lane & 3) + (c & 1);
             const int pos = first_pos + row_lo + (c >> 1) * 8;
-            const bool vis = j <= pos && j >= kv_lo && (window <= 0 || j > pos - window);
+            const bool vis = j <= pos && (window <= 0 || j > pos - window || (XP && j < keep_first));
             if (!vis) v = -INFINITY;
           }
           s[nt][c] = v;
@@ -202,7 +209,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
-                       float scale_log2, int splits, const FusedQK fq, float sink) {
+                       float scale_log2, int splits, const FusedQK fq, float sink, int keep_first) {
   pdl_launch_dependents();
   // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -214,7 +221,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA, XP>(
       smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial, q, q_stride, kcache, vcache,
       block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq,
-      nullptr, &map_k, &map_v, bars, status, sink);
+      nullptr, &map_k, &map_v, bars, status, sink, keep_first);
 }
 
 template <int D>
@@ -235,7 +242,7 @@ template <int D>
 int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const void* kc, const void* vc,
                    const int* bt, int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
                    const int* tile_q0, int n_tiles, int nq, int nkv, int page_size, int window, float scale,
-                   cudaStream_t stream, bool xp = false, float sink = 0.f) {
+                   cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
   auto kern = xp ? attn_prefill_mma_kernel<D, true> : attn_prefill_mma_kernel<D, false>;
   const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * D * 2;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -243,7 +250,8 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   dim3 grid(nq, n_tiles);
   zi_launch(kern, dim3(grid), dim3(PF_THREADS), smem, stream, (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
-                                           page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, sink);
+                                           page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, sink,
+                                           keep_first);
   return zi_check_launch("attention_prefill");
 }
 
@@ -255,7 +263,7 @@ template <int D, bool FUSED, bool TR, bool TMA, bool XP = false>
 int launch_decode_as(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                      const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q,
                      const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window,
-                     float scale, int splits, const FusedQK& fq, cudaStream_t stream, float sink = 0.f) {
+                     float scale, int splits, const FusedQK& fq, cudaStream_t stream, float sink = 0.f, int keep_first = 0) {
   auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA, XP>;
   CUtensorMap map_k, map_v;
   memset(&map_k, 0, sizeof(map_k));
@@ -277,7 +285,8 @@ int launch_decode_as(void* out, int out_stride, float* partial, const void* q, i
   dim3 grid(n_dec, nkv, splits);
   zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, map_k, map_v, status, (bf16*)out, out_stride,
             splits > 1 ? partial : nullptr, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q,
-            kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq, sink);
+            kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq, sink,
+            keep_first);
   return 0;
 }
 
@@ -285,7 +294,7 @@ template <int D, bool FUSED>
 int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                   const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                   const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                  const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f) {
+                  const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
   // Groups of at most 8 query heads take the transposed tile (keys on the MMA's rows).  Keys and values come by
   // TMA (page boxes, pages of 8, 16, 32, ... tokens whose rows a tensor map can address) while the requests
   // are few, and by cp.async from every lane when they are many.  Measured per 36-layer step (Qwen3-8B
@@ -301,7 +310,8 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
                                         dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream)
 #define ZI_DECODE_XP(TR_, TMA_)                                                                                        \
   launch_decode_as<D, false, TR_, TMA_, true>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q,    \
-                                              kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, sink)
+                                              kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, sink, \
+                                              keep_first)
   int rc0;
   if constexpr (!FUSED) {
     if (xp)     // exact weights and a sink: the kernel that only reads q (the fused form makes whole-head rotations)
@@ -328,15 +338,15 @@ template <bool FUSED>
 int dispatch_decode(int d, void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                     const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                     const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                    const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f) {
+                    const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
   if (d == 64)
     return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
+                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
   if (d == 128)
     return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens,
-                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
+                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
   return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink);
+                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
 }
 }  // namespace
 
@@ -387,15 +397,26 @@ extern "C" int zi_attention_prefill_mma_sink(void* out, int out_stride, const vo
                                              const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles,
                                              int nq, int nkv, int d, int page_size, int window, float scale, float sink,
                                              cudaStream_t stream) {
+  return zi_attention_prefill_mma_mask(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                                       tile_seq, tile_q0, n_tiles, nq, nkv, d, page_size, window, 0, scale, sink, stream);
+}
+
+// The same with a window that keeps a request's first keep_first tokens visible.
+extern "C" int zi_attention_prefill_mma_mask(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                             const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                             int nq, int nkv, int d, int page_size, int window, int keep_first, float scale,
+                                             float sink, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (keep_first < 0) return zi_refuse("attention_prefill: %d kept first tokens", keep_first);
   if (!zi_attention_mma_supported(nq, nkv, d, 0)) return zi_refuse("attention_prefill: head_dim %d is not 64 or 128", d);
   if (q_stride % 8 || ((uintptr_t)q % 16)) return zi_refuse("attention_prefill: q rows must be 16-byte aligned");
   if (!(sink >= 0.f)) return zi_refuse("attention_prefill: the sink's weight must not be negative");
   if (d == 64)
     return launch_prefill<64>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
-                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink);
+                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink, keep_first);
   return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
-                             tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink);
+                             tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink, keep_first);
 }
 
 extern "C" int zi_attention_decode_mma_sink(void* out, int out_stride, float* workspace, const void* q, int q_stride,
@@ -403,7 +424,18 @@ extern "C" int zi_attention_decode_mma_sink(void* out, int out_stride, float* wo
                                             const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
                                             const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size,
                                             int window, float scale, int splits, float sink, cudaStream_t stream) {
+  return zi_attention_decode_mma_mask(out, out_stride, workspace, q, q_stride, kcache, vcache, n_pages, block_tables, bt_stride,
+                                      cu_q, kv_lens, dec_seq, n_dec, nq, nkv, d, page_size, window, 0, scale, splits, sink, stream);
+}
+
+extern "C" int zi_attention_decode_mma_mask(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                                            const void* kcache, const void* vcache, long long n_pages,
+                                            const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
+                                            const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size,
+                                            int window, int keep_first, float scale, int splits, float sink,
+                                            cudaStream_t stream) {
   if (n_dec <= 0) return 0;
+  if (keep_first < 0) return zi_refuse("attention_decode: %d kept first tokens", keep_first);
   if (!zi_attention_mma_supported(nq, nkv, d, 1))
     return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
   if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
@@ -411,7 +443,7 @@ extern "C" int zi_attention_decode_mma_sink(void* out, int out_stride, float* wo
   if (!(sink >= 0.f)) return zi_refuse("attention_decode: the sink's weight must not be negative");
   FusedQK none = {};
   return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, n_pages, block_tables, bt_stride, cu_q,
-                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream, true, sink);
+                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream, true, sink, keep_first);
 }
 
 // Floats of workspace a decode launch with `splits` > 1 needs.

@@ -356,7 +356,7 @@ __device__ __forceinline__ void attn_decode_unit(
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
     int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq,
     uint8_t* fused_area = nullptr, const CUtensorMap* map_k = nullptr, const CUtensorMap* map_v = nullptr,
-    uint64_t* bars = nullptr, int* status = nullptr, float sink = 0.f) {
+    uint64_t* bars = nullptr, int* status = nullptr, float sink = 0.f, int keep_first = 0) {
 
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -373,7 +373,13 @@ __device__ __forceinline__ void attn_decode_unit(
   const int* bt = block_tables + (size_t)seq * bt_stride;
 
   const int kt0 = (kv_lo / DC_TILE) * DC_TILE;
-  const int total_tiles = max(0, (kv_hi - kt0 + DC_TILE - 1) / DC_TILE);
+  // with a window, the request's first keep_first keys stay visible: the tiles of those that lie before the
+  // window's first tile are walked first (they count among the tiles that the splits share)
+  // (only in the form with a sink: in the plain form all of this folds away)
+  const int keep_end = XP && window > 0 ? min(keep_first, kv_lo) : 0;
+  const int n_keep = (min(keep_end, kt0) + DC_TILE - 1) / DC_TILE;
+  const int total_tiles = n_keep + max(0, (kv_hi - kt0 + DC_TILE - 1) / DC_TILE);
+  auto tile_key0 = [&](int tile) { return tile < n_keep ? tile * DC_TILE : kt0 + (tile - n_keep) * DC_TILE; };
   const int tps = (total_tiles + splits - 1) / splits;
   const int t_begin = z * tps, t_end = min(total_tiles, t_begin + tps);
   const int n_tiles = max(0, t_end - t_begin);
@@ -397,8 +403,8 @@ __device__ __forceinline__ void attn_decode_unit(
   // Lane r (r < 16) looks up the page of key r of a tile one iteration before the tile's
   // copies are issued, so the block-table load is never waited for inside the loop.
   auto lookup = [&](int t) -> int {
-    const int j = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS + (lane & 15);
-    if (t >= n_tiles || j < kv_lo || j >= kv_hi) return -1;
+    const int j = tile_key0(t_begin + t) + warp * DC_KEYS + (lane & 15);
+    if (t >= n_tiles || (j < kv_lo && j >= keep_end) || j >= kv_hi) return -1;
     return __ldg(bt + (page_shift >= 0 ? (j >> page_shift) : (j / page_size)));
   };
   uint64_t* my_bars = TMA ? bars + warp * STAGES : nullptr;
@@ -413,7 +419,7 @@ __device__ __forceinline__ void attn_decode_unit(
   }
   auto issue = [&](int t, int pg) {   // this warp's 16 keys of tile t into stage t % STAGES
     uint8_t* ks = ring + (t % STAGES) * 2 * ROWS_BYTES;
-    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
+    const int key0 = tile_key0(t_begin + t) + warp * DC_KEYS;
     if constexpr (TMA)
       tma_kv_tile<D>(ks, ks + ROWS_BYTES, &my_bars[t % STAGES], key0, pg, map_k, map_v, nkv, kvh, page_size, lane);
     else
@@ -637,8 +643,8 @@ __device__ __forceinline__ void attn_decode_unit(
       cp_async_wait<STAGES - 1>();
     }
     __syncwarp();
-    const int key0 = kt0 + (t_begin + t) * DC_TILE + warp * DC_KEYS;
-    if (key0 < kv_hi && key0 + DC_KEYS > kv_lo) {
+    const int key0 = tile_key0(t_begin + t) + warp * DC_KEYS;
+    if (key0 < kv_hi && (key0 + DC_KEYS > kv_lo || key0 < keep_end)) {
       const uint32_t ks_addr = smem_addr(ring + (t % STAGES) * 2 * ROWS_BYTES), vs_addr = ks_addr + ROWS_BYTES;
       const bool need_mask = key0 + DC_KEYS > kv_hi || key0 < kv_lo;
       if constexpr (TR) {
@@ -649,7 +655,7 @@ __device__ __forceinline__ void attn_decode_unit(
           float v = st[c] * scale_log2;
           if (need_mask) {
             const int j = key0 + (lane >> 2) + (c >> 1) * 8;
-            if (j >= kv_hi || j < kv_lo) v = -INFINITY;
+            if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;
           }
           st[c] = v;
         }
@@ -699,7 +705,7 @@ __device__ __forceinline__ void attn_decode_unit(
           float v = s[nt][c] * scale_log2;
           if (need_mask) {
             const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
-            if (j >= kv_hi || j < kv_lo) v = -INFINITY;
+            if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;
           }
           s[nt][c] = v;
         }

@@ -1081,15 +1081,22 @@ ATTENTION_BACKEND = os.environ.get("ZINFER_B200_ATTENTION", "auto")   # auto | g
 PREFILL_ATTENTION = os.environ.get("ZINFER_B200_PREFILL_ATTENTION", "tcgen05")
 
 
-def _attention_work(step, decode: bool, num_heads: int, num_kv_heads: int, head_dim: int, elt: int) -> tuple[int, int]:
+def _attention_work(step, decode: bool, num_heads: int, num_kv_heads: int, head_dim: int, elt: int,
+                    window: int = 0, keep_first: int = 0) -> tuple[int, int]:
     """(bytes, flops) of the attention of a step's decode requests (one token) or of its others:
-    every key and value of those requests once, their queries and outputs; 4 d per (query, key) pair."""
+    every key and value that those requests' queries can see once (all of them, or with a window the last
+    ``window`` + q - 1 and the first ``keep_first``), their queries and outputs; 4 d per visible (query, key) pair."""
     nbytes = flops = 0
     for q, c in zip(step.q_lens, step.ctx_lens):
         if (q == 1) != decode:
             continue
-        nbytes += 2 * (c + q) * num_kv_heads * head_dim * elt + 2 * q * num_heads * head_dim * elt
-        flops += 4 * num_heads * head_dim * (q * c + q * (q + 1) // 2)
+        keys = c + q
+        pairs = q * c + q * (q + 1) // 2
+        if window and window > 0:
+            keys = min(keys, window + q - 1 + int(keep_first or 0))
+            pairs = sum(min(p + 1, window + min(int(keep_first or 0), max(0, p + 1 - window))) for p in range(c, c + q))
+        nbytes += 2 * keys * num_kv_heads * head_dim * elt + 2 * q * num_heads * head_dim * elt
+        flops += 4 * num_heads * head_dim * pairs
     return nbytes, flops
 
 
@@ -1109,8 +1116,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     L = lib()
     keep_first = int(keep_first or 0) if window else 0
     same_size = value_dim is None or int(value_dim) == head_dim
-    # the tensor-core kernels take values of the keys' size and no kept first tokens
-    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and not keep_first
+    # the tensor-core kernels take values of the keys' size; kept first tokens only in the form with a sink
+    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and (not keep_first or bool(sink))
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
@@ -1123,28 +1130,28 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
     out = torch.empty((T, num_heads * head_dim), dtype=q.dtype, device=q.device)
     win = int(window or 0)
-    work = lambda decode: _attention_work(step, decode, num_heads, num_kv_heads, head_dim, q.element_size()) \
+    work = lambda decode: _attention_work(step, decode, num_heads, num_kv_heads, head_dim, q.element_size(), win, keep_first) \
         if _prof.ACTIVE is not None else (0, 0)
     if sink:
         # a softmax with a sink: the mma.sync kernels' form whose weights meet the values as two bfloat16 parts (a design
         # that has a sink also wants its softmax weights in 32-bit) and whose denominator counts the sink
         if step.n_pf_tiles > 0:
             with _prof.region("attention (prefill, mma.sync, sink)", *work(False)):
-                _check(L.zi_attention_prefill_mma_sink(
+                _check(L.zi_attention_prefill_mma_mask(
                     _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                     block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
-                    step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale),
+                    step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, keep_first, ctypes.c_float(scale),
                     ctypes.c_float(sink), _stream()), "attention (prefill, sink)")
         if step.n_dec > 0:
             splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(q.device), step.max_kv_len)
             need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
             ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
             with _prof.region("attention (decode, sink)", *work(True)):
-                _check(L.zi_attention_decode_mma_sink(
+                _check(L.zi_attention_decode_mma_mask(
                     _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache),
                     ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
                     _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size, win,
-                    ctypes.c_float(scale), splits, ctypes.c_float(sink), _stream()), "attention (decode, sink)")
+                    keep_first, ctypes.c_float(scale), splits, ctypes.c_float(sink), _stream()), "attention (decode, sink)")
         return out
     if step.n_pf_tiles > 0 and PREFILL_ATTENTION == "tcgen05" and L.zi_attention_prefill_tcgen05_supported(
             num_heads, num_kv_heads, head_dim, page_size, _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache)):
