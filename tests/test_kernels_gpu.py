@@ -659,3 +659,49 @@ def test_a_wait_that_runs_out_is_reported_not_survived_silently():
     o.require_kernel_status_ok("after")
     with pytest.raises(o.KernelError):
         o.selftest_wait_runs_out(code=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(3, 72, 1e-6), (7, 4096, 1e-5), (300, 200, 3e-6), (515, 1024, 1e-5), (260, 8192, 1e-6),
+                                     (270, 8196, 1e-6), (257, 70, 1e-5)])
+def test_sum_of_updates_and_norm_pair(dtype, T, H, eps):
+    """Few rows and many (rows in registers, 16-byte accesses), widths that are no multiple of 4 or too wide for
+    registers, one norm and two, two updates of different types with a scale, a bias, picked rows."""
+    o = ops()
+    h0 = rnd(T, H, scale=3.0)
+    a = rnd(T, H, dtype=dtype, seed=1)
+    b = rnd(T, H, dtype=torch.float32, seed=2)
+    bias = 0.1 * rnd(H, seed=3)
+    w1, w2 = 1 + 0.1 * rnd(H, seed=4), 1 + 0.1 * rnd(H, seed=5)
+
+    def plain(h, total):
+        v = h if total is None else h + total
+        inv = torch.rsqrt((v * v).mean(dim=1, keepdim=True) + eps)
+        return v, (v * inv * w1).to(dtype), (v * inv * w2).to(dtype)
+
+    total = a.float() + 0.5 * b + bias
+    want_h, want1, want2 = plain(h0, total)
+    h = h0.clone()
+    got1, got2 = o.sum_norm(h, o.Several([a, o.Scaled(b, 0.5)]), w1, eps, dtype, w2=w2, bias=bias)
+    torch.testing.assert_close(h, want_h, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(got1, want1, **tol(dtype))
+    torch.testing.assert_close(got2, want2, **tol(dtype))
+    # one norm, no update: the stream stays as it is
+    h = h0.clone()
+    got = o.sum_norm(h, None, w2, eps, dtype)
+    assert torch.equal(h, h0)
+    torch.testing.assert_close(got, plain(h0, None)[2], **tol(dtype))
+    # picked rows (with a repeat): the stream is left alone, the picked rows' norms include the update
+    rows = torch.tensor([T - 1, 0, T - 1] + list(range(0, T, 2)), dtype=torch.int32, device=DEV)
+    h = h0.clone()
+    got1, got2 = o.sum_norm(h, a, w1, eps, dtype, w2=w2, rows=rows)
+    assert torch.equal(h, h0)
+    _, want1, want2 = plain(h0, a.float())
+    torch.testing.assert_close(got1, want1[rows.long()], **tol(dtype))
+    torch.testing.assert_close(got2, want2[rows.long()], **tol(dtype))
+    # the update as split-K partial sums
+    parts = torch.stack([0.25 * a.float(), 0.5 * a.float(), 0.25 * a.float()]).contiguous()
+    h = h0.clone()
+    got1 = o.sum_norm(h, o.Partials(parts), w1, eps, dtype)
+    torch.testing.assert_close(h, h0 + a.float(), rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(got1, want1, **tol(dtype))
