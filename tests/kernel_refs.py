@@ -189,8 +189,10 @@ def qk_norm_rope_store(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weigh
     return qkv
 
 
-def linear(x, weight, out_dtype=None, out=None, allow_partials=False, fresh_weight=False):
+def linear(x, weight, out_dtype=None, out=None, allow_partials=False, fresh_weight=False, relu2=False):
     y = x.to(torch.float32) @ weight.to(torch.float32).T
+    if relu2:
+        y = torch.relu(y) ** 2
     if out is not None:
         out.copy_(y)
         return out

@@ -248,6 +248,28 @@ def test_linear_swiglu_fused_epilogue(M, I, K):
     assert o.kernel_status() == 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 2048, 4096), (8, 96, 12288), (33, 640, 200), (65, 192, 72),
+                                   (300, 512, 264), (2048, 1536, 1024), (7, 45, 17)])
+def test_linear_with_the_square_of_relu(dtype, M, N, K):
+    """The product with relu squared taken on its 32-bit sums: in the epilogue of an unsplit tensor-core product (few
+    tokens and many), where the K splits of a split one are added, and after the CUDA-core product."""
+    o = ops()
+    x = rnd(M, K, dtype=dtype)
+    w = rnd(N, K, dtype=dtype, scale=0.05, seed=1)
+    got = o.linear(x, w, relu2=True)
+    want = torch.relu(x.double() @ w.double().T) ** 2
+    assert got.shape == (M, N) and got.dtype == dtype
+    t = dict(rtol=1e-5, atol=1e-6 * K) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=2e-3)
+    torch.testing.assert_close(got.double(), want, **t)
+    assert (got >= 0).all()
+    # the unfused route agrees
+    torch.testing.assert_close(o.relu2_(o.linear(x, w)).double(), want, **(t if dtype == torch.float32 else dict(rtol=3e-2, atol=4e-3)))
+    with pytest.raises(o.KernelError):
+        o.linear(x, w, relu2=True, allow_partials=True)
+    assert o.kernel_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 1000, 264), (1000, 4096, 512), (2048, 768, 4096),
                                    (2100, 389 * 2, 160)])
 def test_linear_with_the_kernel_for_cta_pairs(M, N, K):

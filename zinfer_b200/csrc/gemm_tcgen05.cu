@@ -563,10 +563,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
-// out[m * ldo + n] = sum over splits of partial[z][m][n], in order of z.
+// out[m * ldo + n] = sum over splits of partial[z][m][n], in order of z; with relu2 the square of the sum's relu.
 template <typename TO>
 __global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restrict__ partial, int M, int N,
-                                     int splits, long long ldo) {
+                                     int splits, long long ldo, int relu2) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -575,6 +575,10 @@ __global__ void splitk_reduce_kernel(TO* __restrict__ out, const float* __restri
   float acc = 0.f;
   for (int z = 0; z < splits; ++z) acc += partial[(size_t)z * total + idx];
   const int m = (int)(idx / N), n = (int)(idx % N);
+  if (relu2) {
+    acc = fmaxf(acc, 0.f);
+    acc *= acc;
+  }
   out[(long long)m * ldo + n] = from_f32<TO>(acc);
 }
 
@@ -851,6 +855,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   g.a_group_cols = a_group_cols;
   g.out_group_stride = out_group_stride;
   g.late_weights = (defer_reduce >> 1) & 1;
+  relu2 = relu2 || ((defer_reduce >> 2) & 1);
   defer_reduce &= 1;
   g.cand_val = cand_val;
   g.cand_idx = cand_idx;
@@ -890,7 +895,11 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
 
   if (tile_group && (swap || g.splits != 1 || epi != EPI_PLAIN))
     return zi_refuse("%s: the grouped product runs unsplit with the tokens on the lanes", what);
-  if (!tile_group && !head_groups && !geglu && use_pair_kernel(plan, M)) {
+  if (relu2 && (epi != EPI_PLAIN || head_groups || (defer_reduce && g.splits > 1)))
+    return zi_refuse("%s: the square of relu goes with the plain product whose splits are added here", what);
+  // a split product's partial sums are squared where they are added, an unsplit one's in the epilogue
+  const int relu2_epi = relu2 && g.splits == 1, relu2_sum = relu2 && g.splits > 1;
+  if (!tile_group && !head_groups && !geglu && !relu2 && use_pair_kernel(plan, M)) {
     ZI_DISPATCH_DTYPE(out_dtype, TO, { return launch_pair<TO>(out, map_a, map_b, g, M, N, K, status, swiglu, what, stream); });
   }
   if (epi == EPI_ARGMAX) {
@@ -901,7 +910,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
   ZI_DISPATCH_DTYPE(out_dtype, TO, {
     const bool ext = g.tile_group || g.late_weights || g.group_tiles;
     const GemmArgs& plain = g;      // the plain product takes its own arguments only
-    int rc = relu2 ? launch_single<TO, EPI_RELU2, GemmExtArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
+    int rc = relu2_epi ? launch_single<TO, EPI_RELU2, GemmExtArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
            : (ext && !swiglu) ? launch_single<TO, EPI_PLAIN, GemmExtArgs>(out, map_a, map_b, g, partial, status, sm_count, smem, total_tiles, what, stream)
            : geglu ? launch_single<TO, EPI_GEGLU, GemmArgs>(out, map_a, map_b, plain, partial, status, sm_count, smem, total_tiles, what, stream)
            : swiglu ? launch_single<TO, EPI_SWIGLU, GemmArgs>(out, map_a, map_b, plain, partial, status, sm_count, smem, total_tiles, what, stream)
@@ -910,7 +919,7 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
     if (partial && !defer_reduce) {
       const size_t total = (size_t)M * N;
       zi_launch(splitk_reduce_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (TO*)out,
-                partial, M, N, g.splits, (long long)ldo);
+                partial, M, N, g.splits, (long long)ldo, relu2_sum);
       rc = zi_check_launch("splitk_reduce");
       if (rc) return rc;
     }
@@ -922,7 +931,8 @@ int launch_gemm(void* out, int out_dtype, const CUtensorMap& map_a, const CUtens
 // With `defer_reduce` (bit 0) and a split product, the partial sums are left in `workspace` as
 // [splits, M, N] floats for a consumer that adds them itself, and `out` is not written.  Bit 1 of
 // `defer_reduce`: w is not a weight but written by an earlier kernel of the step; its tiles are then
-// not requested ahead of the wait for those kernels.
+// not requested ahead of the wait for those kernels.  Bit 2: the square of relu of every result (in the epilogue
+// of an unsplit product, else where the splits are added; not together with bit 0).
 extern "C" int zi_gemm_tcgen05(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int ldx,
                                int ldw, int ldo, float* workspace, long long workspace_bytes, int sm_count,
                                int defer_reduce, cudaStream_t stream) {

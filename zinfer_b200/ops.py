@@ -535,8 +535,10 @@ def _sm_count(device: torch.device) -> int:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None, allow_partials: bool = False, fresh_weight: bool = False):
-    """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation.
+           out: Optional[torch.Tensor] = None, allow_partials: bool = False, fresh_weight: bool = False,
+           relu2: bool = False):
+    """``x [M, K] @ weight [N, K]^T`` with 32-bit accumulation; with ``relu2`` the square of the product's relu
+    (taken on the 32-bit sums: in the tensor-core product's epilogue, or where its K splits are added).
 
     With ``allow_partials`` a product that was split along K may come back as
     :class:`Partials` (its consumer adds the splits) instead of a tensor.  ``fresh_weight``:
@@ -550,6 +552,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     N, K2 = weight.shape
     _need(K == K2, f"linear: x has {K} columns, weight has {K2}")
     _need(x.stride(1) == 1 and weight.stride(1) == 1, "linear: operands must be dense along K")
+    _need(not (relu2 and allow_partials), "linear: partial sums cannot carry the square of relu")
     if (GEMM_BACKEND != "simt" and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M > 0
             and lib().zi_gemm_tcgen05_supported(_ptr(x), _ptr(weight), K, x.stride(0), weight.stride(0))):
         plan = (ctypes.c_int * 3)()
@@ -559,11 +562,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         defer = allow_partials and need > 0 and out is None
         if out is None and not defer:
             out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
-        with _prof.region(f"linear N={N} K={K}", lambda: _nb(weight) + M * K * 2 + (_nb(ws) if defer else _nb(out)),
-                          2 * M * N * K):
+        with _prof.region(f"linear{'+relu2' if relu2 else ''} N={N} K={K}",
+                          lambda: _nb(weight) + M * K * 2 + (_nb(ws) if defer else _nb(out)), 2 * M * N * K):
             _check(lib().zi_gemm_tcgen05(_ptr(out), _tag(out) if out is not None else BF16, _ptr(x), _ptr(weight), M, N, K,
                                          x.stride(0), weight.stride(0), out.stride(0) if out is not None else N, _ptr(ws),
-                                         ctypes.c_longlong(need), sms, (1 if defer else 0) | (2 if fresh_weight else 0),
+                                         ctypes.c_longlong(need), sms,
+                                         (1 if defer else 0) | (2 if fresh_weight else 0) | (4 if relu2 else 0),
                                          _stream()), "linear (tcgen05)")
         return Partials(ws.view(plan[2], M, N)) if defer else out
     if out is None:
@@ -572,6 +576,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     with _prof.region(f"linear (CUDA cores) N={N} K={K}", lambda: _nb(weight, out) + M * K * x.element_size(), 2 * M * N * K):
         _check(lib().zi_gemm_simt(_ptr(out), _tag(out), _ptr(x), _tag(x), _ptr(weight), _tag(weight), M, N, K,
                                   x.stride(0), weight.stride(0), out.stride(0), _stream()), "linear")
+    if relu2:
+        _need(out.is_contiguous(), "linear: the square of relu wants dense results")
+        relu2_(out)
     return out
 
 

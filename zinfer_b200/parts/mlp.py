@@ -73,5 +73,5 @@ class PlainMLP(FeedForward):
         self.w_down = tensors[self.names[1]].contiguous()
 
     def forward(self, x):
-        mid = ops.relu2_(ops.linear(x, self.w_up, out_dtype=self.ctx.dtype))
+        mid = ops.linear(x, self.w_up, out_dtype=self.ctx.dtype, relu2=True)
         return ops.linear(mid, self.w_down, out_dtype=self.ctx.dtype, allow_partials=True)
