@@ -727,3 +727,32 @@ def test_sum_of_updates_and_norm_pair(dtype, T, H, eps):
     got1 = o.sum_norm(h, o.Partials(parts), w1, eps, dtype)
     torch.testing.assert_close(h, h0 + a.float(), rtol=1e-6, atol=1e-6)
     torch.testing.assert_close(got1, want1, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,top,E,N,K,relu2", [(8, 4, 32, 96, 4096, True), (3, 2, 5, 50, 2056, False), (20, 3, 3, 33, 36, True),
+                                              (1, 1, 2, 16, 1024, False), (8, 2, 4, 40, 1288, True)])
+def test_grouped_product_of_few_rows(dtype, T, top, E, N, K, relu2):
+    """The memory-bound grouped product of a decode step: rows of 16-byte and of 8-byte pieces, chunks that end inside
+    a block of columns, experts with no row, one row and more than a tile of rows, columns that are no multiple of 16."""
+    o = ops()
+    g = torch.Generator().manual_seed(T * 131 + K)
+    chosen = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32).to(DEV)
+    x = rnd(T, K, dtype=dtype)
+    w = rnd(E, N, K, dtype=dtype, scale=K ** -0.5, seed=3)
+    row_token, _, _, tile_expert, n_tiles = o.moe_align(chosen, E, 16)
+    out = torch.full((row_token.numel(), N), 7.0, dtype=torch.float32, device=DEV)
+    assert o.linear_few_rows_ok(x, w)
+    o.linear_few_rows(x, w, out, row_token, tile_expert, n_tiles, relu2=relu2)
+    rt, te = row_token.cpu().tolist(), tile_expert.cpu().tolist()
+    seen = 0
+    for r, t in enumerate(rt):
+        if t < 0:
+            continue
+        want = x[t].double() @ w[te[r // 16]].double().T
+        if relu2:
+            want = torch.relu(want) ** 2
+        torch.testing.assert_close(out[r].double(), want, rtol=2e-5, atol=2e-5)
+        seen += 1
+    assert seen == T * top
+    assert o.kernel_status() == 0

@@ -255,13 +255,48 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
 
 // Few rows per expert (a decode step): out[r, n] = act(sum_k x[row_src[r], k] * w[e][n][k]) for the rows r of
 // tile `blockIdx.y` (16 rows, one expert e).  A block takes 16 output columns, a warp two: its lanes stream
-// the weight rows once in 8-byte pieces and multiply them with the tile's rows in use (they come first in
-// a tile), which lie in shared memory as 32-bit values, FR_CHUNK columns at a time.  The weights are read once per tile: bound by memory, not by
-// multiply-adds.  Needs K % 4 == 0.  Every output is one sum in a fixed order (lane-strided, then the
-// lanes' partial sums), independent of the batch.
-constexpr int FR_ROWS = 16, FR_WARPS = 8, FR_PER_WARP = 2, FR_COLS = FR_WARPS * FR_PER_WARP, FR_CHUNK = 1024;
+// the weight rows once, in pieces of VEC values (16 bytes where the row length allows: 8 bfloat16 or 4 floats,
+// else 8 bytes), four pieces of a lane in flight together, with the hint that they are not read again, and
+// multiply them with the tile's rows in use (they come first in a tile), which lie in shared memory as 32-bit
+// values, a chunk of columns at a time (as long as the rows in use leave room for).  With pieces of 8 values a row's chunk lies in shared memory in blocks of
+// 256 columns whose halves of every piece are 128 floats apart, so that a warp's 16-byte reads meet no bank
+// twice.  The weights are read once per tile: bound by memory, not by multiply-adds.  Needs K % 4 == 0.  Every
+// output is one sum in a fixed order (lane-strided, then the lanes' partial sums), independent of the batch.
+constexpr int FR_ROWS = 16, FR_WARPS = 8, FR_PER_WARP = 2, FR_COLS = FR_WARPS * FR_PER_WARP, FR_CHUNK = 1024, FR_UNROLL = 4;
 
-template <typename TX, typename TW, typename TO>
+template <typename T, int VEC> struct FewPiece;
+template <> struct FewPiece<float, 4> {
+  using Raw = float4;
+  static __device__ __forceinline__ Raw ld(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* o) { o[0] = r.x; o[1] = r.y; o[2] = r.z; o[3] = r.w; }
+};
+__device__ __forceinline__ void few_unpack2(uint32_t raw, float* o) {
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw);
+  o[0] = __low2float(a);
+  o[1] = __high2float(a);
+}
+template <> struct FewPiece<__nv_bfloat16, 4> {
+  using Raw = uint2;
+  static __device__ __forceinline__ Raw ld(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint2*>(p)); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* o) { few_unpack2(r.x, o); few_unpack2(r.y, o + 2); }
+};
+template <> struct FewPiece<__nv_bfloat16, 8> {
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw ld(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* o) {
+    few_unpack2(r.x, o); few_unpack2(r.y, o + 2); few_unpack2(r.z, o + 4); few_unpack2(r.w, o + 6);
+  }
+};
+
+// where column k of a row's chunk lies in shared memory (k a multiple of 4)
+template <int VEC>
+__device__ __forceinline__ int few_place(int k) {
+  if (VEC == 4) return k;
+  const int kk = k & 255;
+  return (k & ~255) + ((kk & 4) << 5) + ((kk >> 3) << 2);      // half of the piece * 128 + lane * 4
+}
+
+template <typename TX, typename TW, typename TO, int VEC>
 __global__ void __launch_bounds__(FR_WARPS * 32)
 moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
                     const int* __restrict__ row_src, const int* __restrict__ tile_group,
@@ -269,7 +304,8 @@ moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= *n_tiles_dev) return;
-  extern __shared__ float xs[];            // [FR_ROWS][FR_CHUNK]
+  using Piece = FewPiece<TW, VEC>;
+  extern __shared__ float xs[];            // FR_ROWS * FR_CHUNK floats: [rows in use][chunk]
   __shared__ int src[FR_ROWS];
   __shared__ int n_used;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -293,25 +329,46 @@ moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int
   for (int j = 0; j < FR_PER_WARP; ++j)
 #pragma unroll
     for (int r = 0; r < FR_ROWS; ++r) acc[j][r] = 0.f;
-  for (int k0 = 0; k0 < K; k0 += FR_CHUNK) {
-    const int kc = min(FR_CHUNK, K - k0);
+  constexpr int STEP = 32 * VEC;            // columns a warp takes at a time
+  // the fewer rows are in use, the longer the chunk of each that fits: with up to four rows of 4,096 columns one pass
+  const int chunk = max(FR_CHUNK, (FR_ROWS * FR_CHUNK / used) & ~255);
+  for (int k0 = 0; k0 < K; k0 += chunk) {
+    const int kc = min(chunk, K - k0);
     __syncthreads();     // the chunk before is consumed
     for (int e = threadIdx.x * 4; e < used * kc; e += blockDim.x * 4) {
       const int r = e / kc, k = e - r * kc;
-      *reinterpret_cast<float4*>(xs + r * FR_CHUNK + k) = load4(x + (size_t)src[r] * ldx + k0 + k);
+      *reinterpret_cast<float4*>(xs + r * chunk + few_place<VEC>(k)) = load4(x + (size_t)src[r] * ldx + k0 + k);
     }
     __syncthreads();
-    for (int k = lane * 4; k < kc; k += 128) {
-      float4 wv[FR_PER_WARP];
+    for (int kb = 0; kb < kc; kb += FR_UNROLL * STEP) {
+      typename Piece::Raw raw[FR_UNROLL][FR_PER_WARP];
 #pragma unroll
-      for (int j = 0; j < FR_PER_WARP; ++j) wv[j] = load4(wr[j] + k0 + k);
+      for (int u = 0; u < FR_UNROLL; ++u) {     // every piece of this round is asked for before the first is used
+        const int k = kb + u * STEP + lane * VEC;
 #pragma unroll
-      for (int r = 0; r < FR_ROWS; ++r) {
-        if (r < used) {
-          const float4 xv = *reinterpret_cast<const float4*>(xs + r * FR_CHUNK + k);
+        for (int j = 0; j < FR_PER_WARP; ++j)
+          if (k < kc) raw[u][j] = Piece::ld(wr[j] + k0 + k);
+      }
 #pragma unroll
-          for (int j = 0; j < FR_PER_WARP; ++j)
-            acc[j][r] = fmaf(wv[j].x, xv.x, fmaf(wv[j].y, xv.y, fmaf(wv[j].z, xv.z, fmaf(wv[j].w, xv.w, acc[j][r]))));
+      for (int u = 0; u < FR_UNROLL; ++u) {
+        const int k = kb + u * STEP + lane * VEC;
+        if (k >= kc) continue;
+        float wv[FR_PER_WARP][VEC];
+#pragma unroll
+        for (int j = 0; j < FR_PER_WARP; ++j) Piece::unpack(raw[u][j], wv[j]);
+        const float* xk = xs + (VEC == 4 ? k : (kb + u * STEP) + lane * 4);
+#pragma unroll
+        for (int r = 0; r < FR_ROWS; ++r) {
+          if (r < used) {
+#pragma unroll
+            for (int h = 0; h < VEC / 4; ++h) {
+              const float4 xv = *reinterpret_cast<const float4*>(xk + r * chunk + h * 128);
+#pragma unroll
+              for (int j = 0; j < FR_PER_WARP; ++j)
+                acc[j][r] = fmaf(wv[j][4 * h], xv.x, fmaf(wv[j][4 * h + 1], xv.y,
+                                 fmaf(wv[j][4 * h + 2], xv.z, fmaf(wv[j][4 * h + 3], xv.w, acc[j][r]))));
+            }
+          }
         }
       }
     }
@@ -518,17 +575,20 @@ extern "C" int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x,
   const size_t smem = (size_t)FR_ROWS * FR_CHUNK * sizeof(float);
   dim3 grid((N + FR_COLS - 1) / FR_COLS, max_tiles);
   using bf = __nv_bfloat16;
-#define ZI_FEW(TX, TO)                                                                                             \
+#define ZI_FEW(TX, TO, VEC)                                                                                        \
   do {                                                                                                             \
-    auto kern = moe_few_rows_kernel<TX, TX, TO>;                                                                   \
+    auto kern = moe_few_rows_kernel<TX, TX, TO, VEC>;                                                                 \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)         \
       return zi_refuse("moe_few_rows: cannot get %zu bytes of shared memory", smem);                               \
     zi_launch(kern, dim3(grid), dim3(FR_WARPS * 32), smem, stream, (TO*)out, ldo, (const TX*)x, ldx, (const TX*)w, row_src, \
               tile_group, n_tiles_dev, N, K, relu2);                                                               \
   } while (0)
-  if (dtype == ZI_F32 && out_dtype == ZI_F32) ZI_FEW(float, float);
-  else if (dtype == ZI_BF16 && out_dtype == ZI_F32) ZI_FEW(bf, float);
-  else if (dtype == ZI_BF16 && out_dtype == ZI_BF16) ZI_FEW(bf, bf);
+  const bool wide = K % 8 == 0;        // bfloat16 rows in whole 16-byte pieces
+  if (dtype == ZI_F32 && out_dtype == ZI_F32) ZI_FEW(float, float, 4);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_F32 && wide) ZI_FEW(bf, float, 8);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_F32) ZI_FEW(bf, float, 4);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_BF16 && wide) ZI_FEW(bf, bf, 8);
+  else if (dtype == ZI_BF16 && out_dtype == ZI_BF16) ZI_FEW(bf, bf, 4);
   else return zi_refuse("moe_few_rows: operand type %d with results of type %d", dtype, out_dtype);
 #undef ZI_FEW
   return zi_check_launch("moe_few_rows");
