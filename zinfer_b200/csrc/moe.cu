@@ -6,6 +6,7 @@
 // "identity experts" whose output is their input.  Scores are a softmax over all NR outputs; the
 // choice adds a correction per output to the score, the weight of a chosen expert is its score
 // without the correction, optionally divided by the sum of the chosen scores.
+#include <cstdlib>
 #include "api.h"
 #include "common.cuh"
 
@@ -254,7 +255,7 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
 }
 
 // Few rows per expert (a decode step): out[r, n] = act(sum_k x[row_src[r], k] * w[e][n][k]) for the rows r of
-// tile `blockIdx.y` (16 rows, one expert e).  A block takes 16 output columns, a warp two: its lanes stream
+// tile `blockIdx.y` (16 rows, one expert e).  A block takes groups of 16 output columns, a warp two of each: its lanes stream
 // the weight rows once, in pieces of VEC values (16 bytes where the row length allows: 8 bfloat16 or 4 floats,
 // else 8 bytes), four pieces of a lane in flight together, with the hint that they are not read again, and
 // multiply them with the tile's rows in use (they come first in a tile), which lie in shared memory as 32-bit
@@ -296,20 +297,102 @@ __device__ __forceinline__ int few_place(int k) {
   return (k & ~255) + ((kk & 4) << 5) + ((kk >> 3) << 2);      // half of the piece * 128 + lane * 4
 }
 
+// The block's work for a tile with at most R rows in use (R fixed when compiled, so that a tile of one or two rows
+// carries no arithmetic or tests for sixteen).
+template <typename TX, typename TW, typename TO, int VEC, int R>
+__device__ __forceinline__ void few_rows_run(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int ldx,
+                                             const TW* __restrict__ wbase, const int* src, int used, int r0, int N, int K,
+                                             int relu2, int col_groups, float* xs) {
+  using Piece = FewPiece<TW, VEC>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int STEP = 32 * VEC;            // columns a warp takes at a time
+  // the fewer rows are in use, the longer the chunk of each that fits: with up to four rows of 4,096 columns one pass
+  const int chunk = max(FR_CHUNK, (FR_ROWS * FR_CHUNK / used) & ~255);
+  const bool one_pass = chunk >= K;         // the rows are staged once and serve every column group of the block
+  for (int cg = 0; cg < col_groups; ++cg) {
+    const int nb = (blockIdx.x * col_groups + cg) * FR_COLS;
+    if (nb >= N) break;
+    const int n0 = nb + warp * FR_PER_WARP;
+    const TW* wr[FR_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < FR_PER_WARP; ++j) wr[j] = wbase + (size_t)(n0 + j < N ? n0 + j : 0) * K;
+    float acc[FR_PER_WARP][R];
+#pragma unroll
+    for (int j = 0; j < FR_PER_WARP; ++j)
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[j][r] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += chunk) {
+      const int kc = min(chunk, K - k0);
+      if (!(one_pass && cg > 0)) {
+        __syncthreads();     // the chunk before is consumed
+        for (int e = threadIdx.x * 4; e < used * kc; e += blockDim.x * 4) {
+          const int r = e / kc, k = e - r * kc;
+          *reinterpret_cast<float4*>(xs + r * chunk + few_place<VEC>(k)) = load4(x + (size_t)src[r] * ldx + k0 + k);
+        }
+        __syncthreads();
+      }
+      for (int kb = 0; kb < kc; kb += FR_UNROLL * STEP) {
+        typename Piece::Raw raw[FR_UNROLL][FR_PER_WARP];
+#pragma unroll
+        for (int u = 0; u < FR_UNROLL; ++u) {     // every piece of this round is asked for before the first is used
+          const int k = kb + u * STEP + lane * VEC;
+#pragma unroll
+          for (int j = 0; j < FR_PER_WARP; ++j)
+            if (k < kc) raw[u][j] = Piece::ld(wr[j] + k0 + k);
+        }
+#pragma unroll
+        for (int u = 0; u < FR_UNROLL; ++u) {
+          const int k = kb + u * STEP + lane * VEC;
+          if (k >= kc) continue;
+          float wv[FR_PER_WARP][VEC];
+#pragma unroll
+          for (int j = 0; j < FR_PER_WARP; ++j) Piece::unpack(raw[u][j], wv[j]);
+          const float* xk = xs + (VEC == 4 ? k : (kb + u * STEP) + lane * 4);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            if (R <= 2 || r < used) {       // with R of 1 or 2 every row is in use
+#pragma unroll
+              for (int h = 0; h < VEC / 4; ++h) {
+                const float4 xv = *reinterpret_cast<const float4*>(xk + r * chunk + h * 128);
+#pragma unroll
+                for (int j = 0; j < FR_PER_WARP; ++j)
+                  acc[j][r] = fmaf(wv[j][4 * h], xv.x, fmaf(wv[j][4 * h + 1], xv.y,
+                                   fmaf(wv[j][4 * h + 2], xv.z, fmaf(wv[j][4 * h + 3], xv.w, acc[j][r]))));
+              }
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < FR_PER_WARP; ++j)
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (r >= used) continue;      // uniform in the block
+        float v = warp_sum(acc[j][r]);
+        if (lane == 0 && n0 + j < N) {
+          if (relu2) {
+            v = fmaxf(v, 0.f);
+            v *= v;
+          }
+          out[(size_t)(r0 + r) * ldo + n0 + j] = from_f32<TO>(v);
+        }
+      }
+  }
+}
+
 template <typename TX, typename TW, typename TO, int VEC>
 __global__ void __launch_bounds__(FR_WARPS * 32)
 moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
                     const int* __restrict__ row_src, const int* __restrict__ tile_group,
-                    const int* __restrict__ n_tiles_dev, int N, int K, int relu2) {
+                    const int* __restrict__ n_tiles_dev, int N, int K, int relu2, int col_groups) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= *n_tiles_dev) return;
-  using Piece = FewPiece<TW, VEC>;
   extern __shared__ float xs[];            // FR_ROWS * FR_CHUNK floats: [rows in use][chunk]
   __shared__ int src[FR_ROWS];
   __shared__ int n_used;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r0 = blockIdx.y * FR_ROWS, n0 = blockIdx.x * FR_COLS + warp * FR_PER_WARP;
+  const int r0 = blockIdx.y * FR_ROWS;
   if (threadIdx.x < FR_ROWS) src[threadIdx.x] = row_src[r0 + threadIdx.x];
   __syncthreads();
   if (threadIdx.x == 0) {          // the rows in use come first
@@ -321,72 +404,13 @@ moe_few_rows_kernel(TO* __restrict__ out, int ldo, const TX* __restrict__ x, int
   const int used = n_used;
   if (used == 0) return;
   const TW* wbase = w + (size_t)tile_group[blockIdx.y] * N * K;
-  const TW* wr[FR_PER_WARP];
-#pragma unroll
-  for (int j = 0; j < FR_PER_WARP; ++j) wr[j] = wbase + (size_t)(n0 + j < N ? n0 + j : 0) * K;
-  float acc[FR_PER_WARP][FR_ROWS];
-#pragma unroll
-  for (int j = 0; j < FR_PER_WARP; ++j)
-#pragma unroll
-    for (int r = 0; r < FR_ROWS; ++r) acc[j][r] = 0.f;
-  constexpr int STEP = 32 * VEC;            // columns a warp takes at a time
-  // the fewer rows are in use, the longer the chunk of each that fits: with up to four rows of 4,096 columns one pass
-  const int chunk = max(FR_CHUNK, (FR_ROWS * FR_CHUNK / used) & ~255);
-  for (int k0 = 0; k0 < K; k0 += chunk) {
-    const int kc = min(chunk, K - k0);
-    __syncthreads();     // the chunk before is consumed
-    for (int e = threadIdx.x * 4; e < used * kc; e += blockDim.x * 4) {
-      const int r = e / kc, k = e - r * kc;
-      *reinterpret_cast<float4*>(xs + r * chunk + few_place<VEC>(k)) = load4(x + (size_t)src[r] * ldx + k0 + k);
-    }
-    __syncthreads();
-    for (int kb = 0; kb < kc; kb += FR_UNROLL * STEP) {
-      typename Piece::Raw raw[FR_UNROLL][FR_PER_WARP];
-#pragma unroll
-      for (int u = 0; u < FR_UNROLL; ++u) {     // every piece of this round is asked for before the first is used
-        const int k = kb + u * STEP + lane * VEC;
-#pragma unroll
-        for (int j = 0; j < FR_PER_WARP; ++j)
-          if (k < kc) raw[u][j] = Piece::ld(wr[j] + k0 + k);
-      }
-#pragma unroll
-      for (int u = 0; u < FR_UNROLL; ++u) {
-        const int k = kb + u * STEP + lane * VEC;
-        if (k >= kc) continue;
-        float wv[FR_PER_WARP][VEC];
-#pragma unroll
-        for (int j = 0; j < FR_PER_WARP; ++j) Piece::unpack(raw[u][j], wv[j]);
-        const float* xk = xs + (VEC == 4 ? k : (kb + u * STEP) + lane * 4);
-#pragma unroll
-        for (int r = 0; r < FR_ROWS; ++r) {
-          if (r < used) {
-#pragma unroll
-            for (int h = 0; h < VEC / 4; ++h) {
-              const float4 xv = *reinterpret_cast<const float4*>(xk + r * chunk + h * 128);
-#pragma unroll
-              for (int j = 0; j < FR_PER_WARP; ++j)
-                acc[j][r] = fmaf(wv[j][4 * h], xv.x, fmaf(wv[j][4 * h + 1], xv.y,
-                                 fmaf(wv[j][4 * h + 2], xv.z, fmaf(wv[j][4 * h + 3], xv.w, acc[j][r]))));
-            }
-          }
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < FR_PER_WARP; ++j)
-#pragma unroll
-    for (int r = 0; r < FR_ROWS; ++r) {
-      if (r >= used) continue;      // uniform in the block
-      float v = warp_sum(acc[j][r]);
-      if (lane == 0 && n0 + j < N) {
-        if (relu2) {
-          v = fmaxf(v, 0.f);
-          v *= v;
-        }
-        out[(size_t)(r0 + r) * ldo + n0 + j] = from_f32<TO>(v);
-      }
-    }
+#define ZI_FEW_RUN(R) few_rows_run<TX, TW, TO, VEC, R>(out, ldo, x, ldx, wbase, src, used, r0, N, K, relu2, col_groups, xs)
+  if (used == 1) ZI_FEW_RUN(1);
+  else if (used == 2) ZI_FEW_RUN(2);
+  else if (used <= 4) ZI_FEW_RUN(4);
+  else if (used <= 8) ZI_FEW_RUN(8);
+  else ZI_FEW_RUN(16);
+#undef ZI_FEW_RUN
 }
 
 // One block lays the P = T * top pairs out by expert.  Pairs of expert e take the rows
@@ -573,7 +597,11 @@ extern "C" int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x,
   if (K % 4 || ldx % 4 || (uintptr_t)x % 16 || (uintptr_t)w % 16)
     return zi_refuse("moe_few_rows: rows of %d values (pitch %d) are not whole 16-byte pieces", K, ldx);
   const size_t smem = (size_t)FR_ROWS * FR_CHUNK * sizeof(float);
-  dim3 grid((N + FR_COLS - 1) / FR_COLS, max_tiles);
+  static const int forced = [] { const char* e = getenv("ZINFER_B200_FEW_ROWS_GROUPS"); return e ? atoi(e) : 0; }();
+  // two groups of 16 columns per block: the rows staged once serve both (measured at 8 requests: 91 -> 79 us for 23
+  // experts of 4,096 x 2,048; four groups: no further gain and too few blocks for narrow experts)
+  const int col_groups = forced > 0 ? forced : 2;
+  dim3 grid((N + FR_COLS * col_groups - 1) / (FR_COLS * col_groups), max_tiles);
   using bf = __nv_bfloat16;
 #define ZI_FEW(TX, TO, VEC)                                                                                        \
   do {                                                                                                             \
@@ -581,7 +609,7 @@ extern "C" int zi_moe_few_rows(void* out, int out_dtype, int ldo, const void* x,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)         \
       return zi_refuse("moe_few_rows: cannot get %zu bytes of shared memory", smem);                               \
     zi_launch(kern, dim3(grid), dim3(FR_WARPS * 32), smem, stream, (TO*)out, ldo, (const TX*)x, ldx, (const TX*)w, row_src, \
-              tile_group, n_tiles_dev, N, K, relu2);                                                               \
+              tile_group, n_tiles_dev, N, K, relu2, col_groups);                                                   \
   } while (0)
   const bool wide = K % 8 == 0;        // bfloat16 rows in whole 16-byte pieces
   if (dtype == ZI_F32 && out_dtype == ZI_F32) ZI_FEW(float, float, 4);
