@@ -749,8 +749,11 @@ def linear_few_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ro
     rows = out.shape[0]
     _need(rows % MOE_TILE_ROWS_SMALL == 0 and out.shape[1] == N and out.stride(1) == 1, "linear_few_rows: shapes")
     pairs = max(1, rows - G * MOE_TILE_ROWS_SMALL)
+    # under the profiler the weights of the tiles in use are counted; their number is read from the device when the
+    # profile is summed up, not here, where the read would stall the chain
     with _prof.region(f"linear (grouped, few rows) N={N} K={K}",
-                      lambda: min(G, pairs) * N * K * weight.element_size() + pairs * (K + N) * x.element_size(), 2 * pairs * N * K):
+                      lambda: (lambda: min(G, pairs, int(n_tiles.item())) * N * K * weight.element_size()
+                               + pairs * (K + N) * x.element_size()), 2 * pairs * N * K):
         _check(lib().zi_moe_few_rows(_ptr(out), _tag(out), out.stride(0), _ptr(x), _tag(x), x.stride(0), _ptr(weight),
                                      _ptr(_i32(row_src, "row_src")), _ptr(_i32(tile_group, "tile_group")),
                                      _ptr(_i32(n_tiles, "n_tiles")), rows // MOE_TILE_ROWS_SMALL, N, K, 1 if relu2 else 0,

@@ -58,7 +58,8 @@ class Profiler:
         finally:
             end.record()
             if rec["keep"]:
-                self._records.append((name, start, end, int(nbytes), int(flops)))
+                # a callable is a count that only the device knows yet: it is asked for in summary(), after everything has run
+                self._records.append((name, start, end, nbytes if callable(nbytes) else int(nbytes), int(flops)))
 
     def summary(self) -> dict:
         torch.cuda.synchronize()
@@ -67,7 +68,7 @@ class Profiler:
             c = classes.setdefault(name, {"class": name, "launches": 0, "ms": 0.0, "bytes": 0, "flops": 0})
             c["launches"] += 1
             c["ms"] += start.elapsed_time(end)
-            c["bytes"] += nbytes
+            c["bytes"] += int(nbytes()) if callable(nbytes) else nbytes
             c["flops"] += flops
         rows = sorted(classes.values(), key=lambda c: -c["ms"])
         total = sum(c["ms"] for c in rows)
@@ -116,7 +117,8 @@ _NULL = _Null()
 
 def region(name: str, nbytes=0, flops=0):
     """A timed region if a profiler is active, else a context that does nothing.  ``nbytes``
-    and ``flops`` may be callables, evaluated only when a profiler is active."""
+    and ``flops`` may be callables, evaluated only when a profiler is active; a callable that ``nbytes``
+    returns in turn is kept and evaluated when the profile is summed up (a count still on the device)."""
     if ACTIVE is None:
         return _NULL
     return ACTIVE.region(name, nbytes() if callable(nbytes) else nbytes, flops() if callable(flops) else flops)
