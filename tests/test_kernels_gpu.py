@@ -756,3 +756,31 @@ def test_grouped_product_of_few_rows(dtype, T, top, E, N, K, relu2):
         seen += 1
     assert seen == T * top
     assert o.kernel_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K", [4096, 1032, 20])
+def test_grouped_product_of_few_rows_for_every_count_of_rows(dtype, K):
+    """Experts with 0, 1, 2, ... 17 rows in one launch: every compiled body of the kernel (1, 2, up to 4, 8 and 16 rows in
+    use) with every count it serves, chunks of every length that the rows in use leave room for."""
+    o = ops()
+    counts = [1, 0, 2, 3, 4, 5, 6, 7, 8, 9, 11, 12, 15, 16, 17]
+    E, N = len(counts), 24
+    chosen = torch.tensor([[e] for e, c in enumerate(counts) for _ in range(c)], dtype=torch.int32)
+    chosen = chosen[torch.randperm(chosen.shape[0], generator=torch.Generator().manual_seed(K))].contiguous().to(DEV)
+    T = chosen.shape[0]
+    x = rnd(T, K, dtype=dtype)
+    w = rnd(E, N, K, dtype=dtype, scale=K ** -0.5, seed=3)
+    row_token, _, _, tile_expert, n_tiles = o.moe_align(chosen, E, 16)
+    out = torch.full((row_token.numel(), N), 7.0, dtype=torch.float32, device=DEV)
+    o.linear_few_rows(x, w, out, row_token, tile_expert, n_tiles)
+    rt, te = row_token.cpu().tolist(), tile_expert.cpu().tolist()
+    per_expert = [0] * E
+    for r, t in enumerate(rt):
+        if t < 0:
+            continue
+        e = te[r // 16]
+        assert int(chosen[t, 0]) == e
+        per_expert[e] += 1
+        torch.testing.assert_close(out[r].double(), x[t].double() @ w[e].double().T, rtol=2e-5, atol=2e-5)
+    assert per_expert == counts
