@@ -784,3 +784,35 @@ def test_grouped_product_of_few_rows_for_every_count_of_rows(dtype, K):
         per_expert[e] += 1
         torch.testing.assert_close(out[r].double(), x[t].double() @ w[e].double().T, rtol=2e-5, atol=2e-5)
     assert per_expert == counts
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K,NR,top", [(4096, 32, 4), (200, 6, 2), (1032, 40, 8), (37, 5, 5)])
+def test_router_gives_a_token_the_same_choice_and_weights_alone_and_in_a_prompt(dtype, K, NR, top):
+    """The router's kernel runs prompts several tokens to a block and few tokens one to a block with a warp per
+    output: a token's choice and weights are the same to the last bit either way, and agree with plain arithmetic."""
+    o = ops()
+    T = 77
+    x = rnd(T, K, dtype=dtype)
+    w = rnd(NR, K, dtype=dtype, scale=4.0 * K ** -0.5, seed=1)
+    corr = 0.2 * rnd(NR, seed=2)
+    for kw in (dict(score="sigmoid", scale=2.5, correction=corr), dict(score="softmax", groups=1, keep=1)):
+        c_all, w_all = o.moe_router_grouped(x, w, top, **kw)
+        for lo, hi in ((0, 1), (5, 13), (40, 72), (76, 77)):
+            c, ww = o.moe_router_grouped(x[lo:hi], w, top, **kw)
+            assert torch.equal(c, c_all[lo:hi]) and torch.equal(ww, w_all[lo:hi])
+        z = x.double() @ w.double().T
+        s = torch.sigmoid(z) if kw["score"] == "sigmoid" else torch.softmax(z, dim=-1)
+        pick = s + (corr.double() if "correction" in kw else 0.0)
+        want = torch.topk(pick, top, dim=-1)
+        margin = (want.values[:, -1] - torch.topk(pick, min(top + 1, NR), dim=-1).values[:, -1]) if top < NR else None
+        clear = torch.ones(T, dtype=torch.bool, device=DEV) if margin is None else margin > 1e-3
+        got_sorted = c_all.long().sort(dim=1).values
+        assert torch.equal(got_sorted[clear], want.indices.sort(dim=1).values[clear])
+        got_w = torch.gather(s, 1, c_all.long()) * kw.get("scale", 1.0)
+        torch.testing.assert_close(w_all.double()[clear], got_w[clear], rtol=2e-4, atol=1e-6)
+    # the softmax router with a correction (one block's tokens and single tokens)
+    c_all, w_all = o.moe_router(x, w, corr, top)
+    c, ww = o.moe_router(x[3:4], w, corr, top)
+    assert torch.equal(c, c_all[3:4]) and torch.equal(ww, w_all[3:4])
+    assert o.kernel_status() == 0
