@@ -3,6 +3,7 @@ from .qwen3 import ConfigError, Qwen3Config, qwen3_model_spec
 from .luvavik import LuvavikConfig, luvavik_model_spec
 from .rogosun import RogosunConfig, rogosun_model_spec
 from .vumezen import VumezenConfig, vumezen_model_spec
+from .sepitar import SepitarConfig, sepitar_model_spec
 from .registry import (Family, UnknownArchitecture, family_for, load_config, register_family, registered,
                        unregister_family)
 
@@ -18,7 +19,11 @@ register_family(Family(name="Rogosun", model_type="rogosun", config_class=Rogosu
 register_family(Family(name="Vumezen", model_type="vumezen", config_class=VumezenConfig,
                        model_spec=vumezen_model_spec), replace=True)
 
+register_family(Family(name="Sepitar", model_type="sepitar", config_class=SepitarConfig,
+                       model_spec=sepitar_model_spec), replace=True)
+
 __all__ = [
+    "SepitarConfig", "sepitar_model_spec",
     "VumezenConfig", "vumezen_model_spec",
     "ConfigError", "Family", "LayerSpec", "LuvavikConfig", "ModelSpec", "PartSpec", "Qwen3Config", "luvavik_model_spec", "ScheduleEntry",
     "UnknownArchitecture", "default_schedule", "family_for", "load_config", "qwen3_model_spec",

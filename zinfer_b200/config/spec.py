@@ -48,11 +48,15 @@ class ScheduleEntry:
     order writes it and the later ones only read it.  ``None`` gives the entry a
     cache of its own.  ``pre_add`` names a row of one of the model's ``tables``
     (name, row): that vector is added to the residual stream right before this run.
+    ``pre_add_input``: the embedding's output (the stream as it was before the first layer) is
+    added to the stream right before this run (a stack that feeds its input in again at the
+    start of every further pass over a range of layers).
     """
 
     layer: int
     cache: Optional[str] = None
     pre_add: Optional[tuple[str, int]] = None
+    pre_add_input: bool = False
 
 
 @dataclass(frozen=True)

@@ -129,6 +129,35 @@ int zi_paged_attention_mask(void* out, int out_stride, const void* q, int q_stri
                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
                             int d, int dv, int v_row, int page_size, int window, int keep_first, float scale,
                             int skip_from, int skip_single, float sink, cudaStream_t stream);
+// The same with changes to the score: sink_logit [heads] (exp(sink_logit[h]) joins head h's denominator), softcap c
+// (s <- c tanh(s / c) after the scale), dist_bias [heads][n_dist] (added by the distance query - key, after the cap;
+// distances from n_dist - 1 on share the last entry).  Each is off when null or 0.
+int zi_paged_attention_mods(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* kcache,
+                            const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                            const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                            int d, int dv, int v_row, int page_size, int window, int keep_first, float scale,
+                            int skip_from, int skip_single, float sink, const float* sink_logit, float softcap,
+                            const float* dist_bias, int n_dist, cudaStream_t stream);
+// A fused projection row [q heads | k heads | v heads | gate]: biases, an RMS norm over all of q and over all of k
+// (weights per element), rotation of the first rot_dims dimensions of every q and k head, q and the gate columns into
+// tensors of their own, k and v into the token's page slot.  The source may be 32-bit beside 16-bit results.
+int zi_qkv_rows_prepare(const void* src, int src_dtype, int src_stride, const float* bias, void* q_out, int q_stride,
+                        void* gate_out, int gate_stride, int n_gate, int out_dtype, int T, int nq, int nkv, int d, int dv,
+                        const float* qw, const float* kw, float eps, int rot_dims, const float* cos_t, const float* sin_t,
+                        int n_table_pos, const int* positions, void* kcache, void* vcache, const int* slots, int page_size,
+                        cudaStream_t stream);
+// RMS norm of rows of activations: out[t] = x[t] * w / sqrt(mean(x[t]^2) + eps).
+int zi_rmsnorm_rows(void* out, int ldo, int out_dtype, const void* x, int ldx, int x_dtype, const float* w, float eps, int T,
+                    int n, cudaStream_t stream);
+// cos/sin [n_pos, half] of pos * freq[i], both times `magnitude`.
+int zi_rope_table_freqs(float* cos_t, float* sin_t, int n_pos, int half, const float* freq, float magnitude,
+                        cudaStream_t stream);
+int zi_sigmoid_gate_grouped(void* out, int ldo, const void* x, int ldx, const void* g, int ldg, int dtype, int T, int width,
+                            int group, cudaStream_t stream);
+// out = g' * sigmoid(alpha g') * (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+int zi_clamped_gate(void* out, int dtype, const void* gu, int gu_dtype, const float* partials, int splits,
+                    long long split_stride, int T, int I, int interleave, float limit, float alpha, float shift,
+                    cudaStream_t stream);
 // q/k norm, rotation of the first rot_dims dimensions of a head, page write; values of their own or the keys as projected.
 int zi_qk_prepare(const void* src, int dtype, int T, int src_stride, void* q_out, int q_stride, int nq, int nkv, int d,
                   int rot_dims, const float* qw, const float* kw, float eps, const float* cos_t, const float* sin_t,
@@ -181,12 +210,21 @@ int zi_moe_router_grouped_c(int* chosen, float* weight, const void* x, int x_dty
 int zi_moe_route_grouped_c(int* chosen, float* weight, const float* logits, const float* correction, int T, int NR, int top,
                            int renormalize, int score_kind, int groups, int keep, float wscale, cudaStream_t stream);
 // Latent attention: the cached row [normed latent | rotated key part] and the rotated query part of a token.
+// Router by the logits themselves: z = W x + bias, the `top` largest chosen, weights = softmax over the chosen logits.
+int zi_moe_router_top_logits(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
+                             const float* bias, int T, int K, int NR, int top, cudaStream_t stream);
+int zi_moe_route_top_logits(int* chosen, float* weight, const float* logits, const float* bias, int T, int NR, int top,
+                            cudaStream_t stream);
 int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank, int rot_dims,
                       const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
                       const int* positions, void* q_eff, void* cache, const int* slots, int write_cache,
                       cudaStream_t stream);
 // For a prompt's portion on the tensor cores: a request's cached rows gathered ([kv_pad, D], and the first `rank`
 // columns transposed [rank, kv_pad]), and the causal softmax of the portion's score matrix.
+int zi_latent_prepare_rows(const void* q, int ldq, int q_dtype, const void* kv, int ldkv, int kv_dtype, int out_dtype, int T,
+                           int heads, int dim, int rd, int rank, int rot_dims, int neighbours, const float* cw, float eps,
+                           const float* cos_t, const float* sin_t, int n_table_pos, const int* positions, void* q_eff,
+                           void* cache, const int* slots, int write_cache, cudaStream_t stream);
 int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, const int* block_table, int page_size,
                      int kv_len, int kv_pad, int D, int rank, cudaStream_t stream);
 int zi_causal_softmax(void* P, const float* S, int dtype, long long rows, int heads, int ctx, int kv_pad, float scale,

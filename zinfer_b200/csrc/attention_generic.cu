@@ -20,6 +20,9 @@ constexpr int BQ = 16, BK = 32, THREADS = 128, ROWS_PER_WARP = BQ / (THREADS / 3
 // serves as key and, in its first dv columns, as value): dv value columns are read from rows of
 // v_row elements in `vcache`; the output has dv columns per head.  MAXJ * 32 bounds dv.
 // With a window, query i sees key j <= i if i - j < window or j < keep_first.
+// Changes to the score, each off unless given: softcap c (s <- c tanh(s / c) after the scale), dist_bias
+// [heads][n_dist] (a bias by the distance i - j, distances from n_dist - 1 on share the last entry; added after
+// the cap), sink_logit [heads] (exp(sink_logit[h]) joins head h's denominator; it has no value).
 template <typename T, int MAXJ>
 __global__ void __launch_bounds__(THREADS)
 paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride,
@@ -27,7 +30,9 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                        const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int nq, int nkv, int d, int page_size, int window,
-                       float scale, int dv, int v_row, int skip_from, int skip_single, float sink, int keep_first) {
+                       float scale, int dv, int v_row, int skip_from, int skip_single, float sink, int keep_first,
+                       const float* __restrict__ sink_logit, float softcap, const float* __restrict__ dist_bias,
+                       int n_dist) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -104,8 +109,10 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
       float s = 0.f;
       for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
       s *= scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
       const bool visible = j <= pos && (window <= 0 || j > pos - window || j < keep_first);
       if (!visible) s = -INFINITY;
+      else if (dist_bias) s += dist_bias[(size_t)h * n_dist + min(pos - j, n_dist - 1)];   // not scaled, not capped
       const float m_new = fmaxf(m[i], warp_max(s));
       float p = 0.f;
       if (m_new != -INFINITY) {
@@ -138,7 +145,8 @@ paged_attention_kernel(T* __restrict__ out, int out_stride, const T* __restrict_
     const int r = warp * ROWS_PER_WARP + i;
     if (r >= nqv) continue;
     // a sink: `sink` keys whose score is 0 and which have no value, counted in the denominator only
-    const float inv = 1.0f / (sink > 0.f ? l[i] + sink * expf(-m[i]) : l[i]);
+    // a learned sink: exp(sink_logit[h]) in the denominator, neither scaled nor capped
+    const float inv = 1.0f / (sink_logit ? l[i] + expf(sink_logit[h] - m[i]) : (sink > 0.f ? l[i] + sink * expf(-m[i]) : l[i]));
     T* o = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * dv;
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) {
@@ -188,7 +196,23 @@ extern "C" int zi_paged_attention_mask(void* out, int out_stride, const void* q,
                                        int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
                                        int keep_first, float scale, int skip_from, int skip_single, float sink,
                                        cudaStream_t stream) {
+  return zi_paged_attention_mods(out, out_stride, q, q_stride, dtype, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                                 tile_seq, tile_q0, n_tiles, nq, nkv, d, dv, v_row, page_size, window, keep_first, scale,
+                                 skip_from, skip_single, sink, nullptr, 0.f, nullptr, 0, stream);
+}
+
+// The same with the changes to the score: a learned sink per head, a cap, a bias by distance.
+extern "C" int zi_paged_attention_mods(void* out, int out_stride, const void* q, int q_stride, int dtype,
+                                       const void* kcache, const void* vcache, const int* block_tables, int bt_stride,
+                                       const int* cu_q, const int* kv_lens, const int* tile_seq, const int* tile_q0,
+                                       int n_tiles, int nq, int nkv, int d, int dv, int v_row, int page_size, int window,
+                                       int keep_first, float scale, int skip_from, int skip_single, float sink,
+                                       const float* sink_logit, float softcap, const float* dist_bias, int n_dist,
+                                       cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (!(softcap >= 0.f)) return zi_refuse("paged_attention: the cap on the scores must not be negative");
+  if (dist_bias && n_dist <= 0) return zi_refuse("paged_attention: a bias by distance needs a table");
+  if (sink_logit && sink != 0.f) return zi_refuse("paged_attention: a learned sink and a counted sink exclude each other");
   if (keep_first < 0) return zi_refuse("paged_attention: %d kept first tokens", keep_first);
   if (!(sink >= 0.f)) return zi_refuse("paged_attention: the sink's weight must not be negative");
   constexpr int WIDE = 20;   // value columns up to 640 (latent caches); 8 serves every ordinary head size
@@ -207,7 +231,8 @@ extern "C" int zi_paged_attention_mask(void* out, int out_stride, const void* q,
     }                                                                                                              \
     zi_launch(kern, dim3(grid), dim3(THREADS), smem, stream, (TT*)out, out_stride, (const TT*)q, q_stride,         \
               (const TT*)kcache, (const TT*)vcache, block_tables, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, \
-              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single, sink, keep_first);              \
+              nkv, d, page_size, window, scale, dv, v_row, skip_from, skip_single, sink, keep_first, sink_logit,    \
+              softcap, dist_bias, n_dist);                                                                         \
   } while (0)
   ZI_DISPATCH_DTYPE(dtype, TT, {
     if (dv <= 256) ZI_LAUNCH_ATTN(8);

@@ -480,6 +480,56 @@ __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu,
   }
 }
 
+// The clamped gate: g <- min(g, limit), u <- clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + shift).
+// gate and up come whole or as split-K partial sums added in order; any width.
+template <typename T, typename TS>
+__global__ void clamped_gate_kernel(T* __restrict__ out, const TS* __restrict__ gu, const float* __restrict__ part, int splits,
+                                    size_t zstride, int I, size_t total, int interleave, float limit, float alpha,
+                                    float shift) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx - t * I);
+  int gc, uc;
+  gate_up_columns(i, I, interleave, gc, uc);
+  float g, u;
+  if (part) {
+    g = u = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      g += part[(size_t)z * zstride + t * 2 * I + gc];
+      u += part[(size_t)z * zstride + t * 2 * I + uc];
+    }
+  } else {
+    g = to_f32(gu[t * 2 * I + gc]);
+    u = to_f32(gu[t * 2 * I + uc]);
+  }
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  out[idx] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+extern "C" int zi_clamped_gate(void* out, int dtype, const void* gu, int gu_dtype, const float* partials, int splits,
+                               long long split_stride, int T, int I, int interleave, float limit, float alpha, float shift,
+                               cudaStream_t stream) {
+  if (interleave && (interleave % 8 || I % interleave)) return zi_refuse("clamped_gate: interleave %d does not fit I = %d", interleave, I);
+  if (!(limit > 0.f)) return zi_refuse("clamped_gate: the limit must be positive");
+  if ((gu == nullptr) == (partials == nullptr)) return zi_refuse("clamped_gate: gate and up come whole or as partial sums");
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  ZI_DISPATCH_DTYPE(dtype, TT, {
+    if (partials || gu_dtype == ZI_F32)
+      zi_launch(clamped_gate_kernel<TT, float>, dim3(blocks), dim3(256), 0, stream, (TT*)out, (const float*)gu, partials, splits,
+                (size_t)split_stride, I, total, interleave, limit, alpha, shift);
+    else
+      zi_launch(clamped_gate_kernel<TT, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (TT*)out, (const __nv_bfloat16*)gu,
+                partials, splits, (size_t)split_stride, I, total, interleave, limit, alpha, shift);
+  });
+  return zi_check_launch("clamped_gate");
+}
+
 #define ZI_DISPATCH_ACT(act, ACT, ...)                                              \
   do {                                                                             \
     if ((act) == ZI_ACT_SILU) { constexpr int ACT = ZI_ACT_SILU; __VA_ARGS__; }     \
@@ -555,6 +605,31 @@ extern "C" int zi_rope_table_scaled(float* cos_t, float* sin_t, int n_pos, int d
   zi_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, cos_t, sin_t, n_pos, d / 2, d, theta,
             factor);
   return zi_check_launch("rope_table");
+}
+
+// cos/sin [n_pos, half] of the angles pos * freq[i] for frequencies the caller made (a model's own rescaling of
+// them), both multiplied by `magnitude`: the angle is a 32-bit product, cos and sin are evaluated in double and
+// rounded once.
+__global__ void rope_table_freqs_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t, int n_pos, int half,
+                                        const float* __restrict__ freq, float magnitude) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)n_pos * half) return;
+  const int pos = (int)(idx / half), i = (int)(idx % half);
+  const float angle = (float)pos * freq[i];
+  cos_t[idx] = (float)(cos((double)angle) * (double)magnitude);
+  sin_t[idx] = (float)(sin((double)angle) * (double)magnitude);
+}
+
+extern "C" int zi_rope_table_freqs(float* cos_t, float* sin_t, int n_pos, int half, const float* freq, float magnitude,
+                                   cudaStream_t stream) {
+  if (half <= 0 || !freq) return zi_refuse("rope_table: no frequencies");
+  const size_t total = (size_t)n_pos * half;
+  if (total == 0) return 0;
+  zi_launch(rope_table_freqs_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, cos_t, sin_t, n_pos, half, freq,
+            magnitude);
+  return zi_check_launch("rope_table_freqs");
 }
 
 extern "C" int zi_rope_table(float* cos_t, float* sin_t, int n_pos, int d, float theta, cudaStream_t stream) {
@@ -1321,22 +1396,29 @@ extern "C" int zi_scale_f32(float* x, long long n, float s, cudaStream_t stream)
 // out[t, c] = x[t, c] * sigmoid(g[t, c]) for rows of `width` values with free row pitches (an output gate).
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ out, int ldo, const T* __restrict__ x, int ldx, const T* __restrict__ g,
-                                    int ldg, int width, size_t total) {
+                                    int ldg, int width, size_t total, int group) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / width;
   const int c = (int)(idx - t * width);
-  const float gv = to_f32(g[t * ldg + c]);
+  const float gv = to_f32(g[t * ldg + c / group]);
   out[t * ldo + c] = from_f32<T>(to_f32(x[t * ldx + c]) / (1.0f + expf(-gv)));
 }
 
 extern "C" int zi_sigmoid_gate(void* out, int ldo, const void* x, int ldx, const void* g, int ldg, int dtype, int T,
                                int width, cudaStream_t stream) {
+  return zi_sigmoid_gate_grouped(out, ldo, x, ldx, g, ldg, dtype, T, width, 1, stream);
+}
+
+// The same with one gate value for every `group` neighbouring columns (a gate per head): g has width / group columns.
+extern "C" int zi_sigmoid_gate_grouped(void* out, int ldo, const void* x, int ldx, const void* g, int ldg, int dtype, int T,
+                                       int width, int group, cudaStream_t stream) {
   const size_t total = (size_t)T * width;
   if (total == 0) return 0;
+  if (group <= 0 || width % group) return zi_refuse("sigmoid_gate: %d columns do not form groups of %d", width, group);
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(sigmoid_gate_kernel<TT>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                                         (TT*)out, ldo, (const TT*)x, ldx, (const TT*)g, ldg, width, total));
+                                         (TT*)out, ldo, (const TT*)x, ldx, (const TT*)g, ldg, width, total, group));
   return zi_check_launch("sigmoid_gate");
 }

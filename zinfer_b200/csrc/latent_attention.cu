@@ -11,44 +11,57 @@
 #include "common.cuh"
 
 namespace {
-// One block per token.  src row: [q heads, each (dim plain | rd rotated)] [rank latent | rd key part].
-// Rotary: of the rd values the first rot_dims are rotated (pairs (i, i + rot_dims/2)), the rest pass.
+// One block per token.  q row: [heads, each (dim plain | rd rotated)]; kv row: [rank latent | rd key part].
+// Rotary: of the rd values the first rot_dims are rotated, in pairs (i, i + rot_dims/2) or, with `neighbours`,
+// in pairs (2i, 2i + 1); the rest pass.  The q row may be 32-bit or of the results' type; so may the kv row.
 template <typename T>
+__device__ __forceinline__ float turned(const T* x, int i, int rot_dims, int neighbours, const float* cs, const float* sn) {
+  float v = to_f32(x[i]);
+  if (i >= rot_dims) return v;
+  const int half = rot_dims >> 1;
+  if (neighbours) {
+    const int p = i >> 1;
+    float a = to_f32(x[2 * p]), b = to_f32(x[2 * p + 1]);
+    rotate_pair(a, b, cs[p], sn[p]);
+    return (i & 1) ? b : a;
+  }
+  if (i < half) {
+    float a = v, b = to_f32(x[i + half]);
+    rotate_pair(a, b, cs[i], sn[i]);
+    return a;
+  }
+  float a = to_f32(x[i - half]), b = v;
+  rotate_pair(a, b, cs[i - half], sn[i - half]);
+  return b;
+}
+
+template <typename TQ, typename TS, typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ src, int ld, int heads, int dim, int rd, int rank, int rot_dims,
-                      const float* __restrict__ cw, float eps, const float* __restrict__ cos_t,
-                      const float* __restrict__ sin_t, int n_table_pos, const int* __restrict__ positions,
-                      T* __restrict__ q_eff, T* __restrict__ cache, const int* __restrict__ slots, int write_cache) {
+latent_prepare_kernel(const TQ* __restrict__ qsrc, int ldq, const TS* __restrict__ kvsrc, int ldkv, int heads, int dim, int rd,
+                      int rank, int rot_dims, int neighbours, const float* __restrict__ cw, float eps,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_table_pos,
+                      const int* __restrict__ positions, T* __restrict__ q_eff, T* __restrict__ cache,
+                      const int* __restrict__ slots, int write_cache) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  const T* row = src + (size_t)t * ld;
   const int D = rank + rd, half = rot_dims / 2;
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= n_table_pos ? n_table_pos - 1 : pos);   // callers keep positions inside the table
   const float* cs = cos_t + (size_t)pos * half;
   const float* sn = sin_t + (size_t)pos * half;
   // the rotated part of every query head -> q_eff[t, h, rank ..]
+  const TQ* qrow = qsrc + (size_t)t * ldq;
   for (int e = threadIdx.x; e < heads * rd; e += blockDim.x) {
     const int h = e / rd, i = e - h * rd;
-    const T* qr = row + (size_t)h * (dim + rd) + dim;
-    float v = to_f32(qr[i]);
-    if (i < half) {
-      float x = v, y = to_f32(qr[i + half]);
-      rotate_pair(x, y, cs[i], sn[i]);
-      v = x;
-    } else if (i < rot_dims) {
-      float x = to_f32(qr[i - half]), y = v;
-      rotate_pair(x, y, cs[i - half], sn[i - half]);
-      v = y;
-    }
-    q_eff[((size_t)t * heads + h) * D + rank + i] = from_f32<T>(v);
+    q_eff[((size_t)t * heads + h) * D + rank + i] =
+        from_f32<T>(turned(qrow + (size_t)h * (dim + rd) + dim, i, rot_dims, neighbours, cs, sn));
   }
   if (!write_cache) return;
   const int slot = slots[t];
   if (slot < 0) return;      // a row that pads a captured batch
-  const T* kv = row + (size_t)heads * (dim + rd);
+  const TS* kv = kvsrc + (size_t)t * ldkv;
   float ss = 0.f;
   for (int i = threadIdx.x; i < rank; i += blockDim.x) {
     const float v = to_f32(kv[i]);
@@ -57,19 +70,7 @@ latent_prepare_kernel(const T* __restrict__ src, int ld, int heads, int dim, int
   const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
   T* out = cache + (size_t)slot * D;
   for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = from_f32<T>(norm_scale(to_f32(kv[i]), cw[i], inv));
-  for (int i = threadIdx.x; i < rd; i += blockDim.x) {
-    float v = to_f32(kv[rank + i]);
-    if (i < half) {
-      float x = v, y = to_f32(kv[rank + i + half]);
-      rotate_pair(x, y, cs[i], sn[i]);
-      v = x;
-    } else if (i < rot_dims) {
-      float x = to_f32(kv[rank + i - half]), y = v;
-      rotate_pair(x, y, cs[i - half], sn[i - half]);
-      v = y;
-    }
-    out[rank + i] = from_f32<T>(v);
-  }
+  for (int i = threadIdx.x; i < rd; i += blockDim.x) out[rank + i] = from_f32<T>(turned(kv + rank, i, rot_dims, neighbours, cs, sn));
 }
 
 // A request's cached rows, gathered from its pages for the tensor-core products of a prompt's portion:
@@ -375,12 +376,34 @@ extern "C" int zi_latent_prepare(const void* src, int ld, int dtype, int T, int 
                                  int rot_dims, const float* cw, float eps, const float* cos_t, const float* sin_t,
                                  int n_table_pos, const int* positions, void* q_eff, void* cache, const int* slots,
                                  int write_cache, cudaStream_t stream) {
+  const size_t elt = dtype == ZI_F32 ? 4 : 2;
+  return zi_latent_prepare_rows(src, ld, dtype, (const char*)src + (size_t)heads * (dim + rd) * elt, ld, dtype, dtype, T, heads,
+                                dim, rd, rank, rot_dims, 0, cw, eps, cos_t, sin_t, n_table_pos, positions, q_eff, cache, slots,
+                                write_cache, stream);
+}
+
+// The same with the queries and the [latent | key part] rows in tensors of their own (queries that come from a
+// projection of their own), each 32-bit or of the results' type, and with the rotation's pairs either (i, i + half)
+// or, with `neighbours`, (2i, 2i + 1).
+extern "C" int zi_latent_prepare_rows(const void* q, int ldq, int q_dtype, const void* kv, int ldkv, int kv_dtype, int out_dtype,
+                                      int T, int heads, int dim, int rd, int rank, int rot_dims, int neighbours,
+                                      const float* cw, float eps, const float* cos_t, const float* sin_t, int n_table_pos,
+                                      const int* positions, void* q_eff, void* cache, const int* slots, int write_cache,
+                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot_dims < 0 || rot_dims % 2 || rot_dims > rd) return zi_refuse("latent_prepare: %d rotated dimensions of %d", rot_dims, rd);
   if (n_table_pos <= 0 && rot_dims > 0) return zi_refuse("latent_prepare: the rotary table is empty");
-  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(latent_prepare_kernel<TT>, dim3(T), dim3(128), 0, stream, (const TT*)src, ld, heads,
-                                         dim, rd, rank, rot_dims, cw, eps, cos_t, sin_t, n_table_pos, positions,
-                                         (TT*)q_eff, (TT*)cache, slots, write_cache));
+#define ZI_LP(TQ, TS, TT)                                                                                               \
+  zi_launch(latent_prepare_kernel<TQ, TS, TT>, dim3(T), dim3(128), 0, stream, (const TQ*)q, ldq, (const TS*)kv, ldkv, heads, \
+            dim, rd, rank, rot_dims, neighbours, cw, eps, cos_t, sin_t, n_table_pos, positions, (TT*)q_eff, (TT*)cache, slots, \
+            write_cache)
+  using bf = __nv_bfloat16;
+  if (out_dtype == ZI_F32 && q_dtype == ZI_F32 && kv_dtype == ZI_F32) ZI_LP(float, float, float);
+  else if (out_dtype == ZI_BF16 && q_dtype == ZI_BF16 && kv_dtype == ZI_BF16) ZI_LP(bf, bf, bf);
+  else if (out_dtype == ZI_BF16 && q_dtype == ZI_BF16 && kv_dtype == ZI_F32) ZI_LP(bf, float, bf);
+  else if (out_dtype == ZI_BF16 && q_dtype == ZI_F32 && kv_dtype == ZI_F32) ZI_LP(float, float, bf);
+  else return zi_refuse("latent_prepare: sources of types %d and %d cannot become results of type %d", q_dtype, kv_dtype, out_dtype);
+#undef ZI_LP
   return zi_check_launch("latent_prepare");
 }
 

@@ -170,6 +170,56 @@ __device__ __forceinline__ void route_token_grouped(int* __restrict__ chosen, fl
   }
 }
 
+// The choice by the logits themselves: z + bias, the `top` largest chosen (ties to the lower index), and the
+// weights are the softmax over the chosen logits only.  score: NR floats of shared memory for this warp.
+__device__ __forceinline__ void route_token_top_logits(int* __restrict__ chosen, float* __restrict__ weight, const float* z,
+                                                       float* score, const float* __restrict__ bias, int t, int NR, int top,
+                                                       int lane) {
+  for (int j = lane; j < NR; j += 32) score[j] = z[j] + (bias ? bias[j] : 0.f);
+  __syncwarp();
+  float first = 0.f, total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int j = lane; j < NR; j += 32) {
+      const float v = score[j];
+      if (v > best) { best = v; arg = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;
+    if (k == 0) first = best;                 // the largest: the softmax's reference
+    const float e = expf(best - first);
+    total += e;
+    if (lane == 0) {
+      chosen[(size_t)t * top + k] = arg;
+      weight[(size_t)t * top + k] = e;
+      score[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float r = 1.0f / total;
+    for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] *= r;
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_top_logits_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits,
+                            const float* __restrict__ bias, int T, int NR, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T) return;
+  route_token_top_logits(chosen, weight, logits + (size_t)t * NR, sm + (size_t)warp * NR, bias, t, NR, top, lane);
+}
+
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_grouped_kernel(int* __restrict__ chosen, float* __restrict__ weight, const float* __restrict__ logits, int T,
                          int NR, int top, int renormalize, int score_kind, int groups, int keep, float wscale,
@@ -203,8 +253,9 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, const flo
 // partial sums meet in a fixed order that depends neither on the other tokens nor on the number of warps), then a
 // warp per token chooses.  Prompts run blocks of 8 warps; a decode step runs up to 32 warps per token, one output
 // each (23 -> 15 us for 8 tokens, 32 outputs, rows of 4,096).  32-bit multiply-adds whatever the operands' types.
-// GROUPED: the choice among groups of outputs (route_token_grouped) instead of the softmax with a correction.
-template <typename TX, typename TW, bool GROUPED, int TOK, bool WIDE>
+// MODE 1: the choice among groups of outputs (route_token_grouped) instead of the softmax with a correction (0);
+// MODE 2: the choice by the logits plus a bias with a softmax over the chosen (route_token_top_logits).
+template <typename TX, typename TW, int MODE, int TOK, bool WIDE>
 __global__ void __launch_bounds__(WIDE ? 1024 : 256)
 moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX* __restrict__ x, int ldx,
                   const TW* __restrict__ w, const float* __restrict__ correction, int T, int K, int NR, int top,
@@ -277,7 +328,9 @@ moe_router_kernel(int* __restrict__ chosen, float* __restrict__ weight, const TX
   __syncthreads();
   for (int i = warp; i < n_tok; i += warps) {
     float* z = zs + (size_t)i * 4 * NR;
-    if (GROUPED)
+    if (MODE == 2)
+      route_token_top_logits(chosen, weight, z, z + NR, correction, t0 + i, NR, top, lane);     // `correction` carries the bias
+    else if (MODE == 1)
       route_token_grouped(chosen, weight, z, z + NR, z + 2 * NR, z + 3 * NR, t0 + i, NR, top, renormalize, score_kind, groups,
                           keep, wscale, lane, correction);
     else
@@ -566,8 +619,9 @@ extern "C" int zi_moe_route_grouped_c(int* chosen, float* weight, const float* l
 }
 
 static int launch_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
-                             const float* correction, int T, int K, int NR, int top, int renormalize, bool grouped,
+                             const float* correction, int T, int K, int NR, int top, int renormalize, int mode,
                              int score_kind, int groups, int keep, float wscale, cudaStream_t stream) {
+  const bool grouped = mode == 1;
   if (T <= 0) return 0;
   if (top <= 0 || top > NR) return zi_refuse("moe_router: %d of %d outputs cannot be chosen", top, NR);
   if (grouped) {
@@ -593,7 +647,7 @@ static int launch_moe_router(int* chosen, float* weight, const void* x, int x_dt
               NR, top, renormalize, score_kind, groups, keep, wscale);                                             \
   } while (0)
 #define ZI_ROUTER_G(TX, TW, GG) do { if (threads > 256) ZI_ROUTER_T(TX, TW, GG, true); else ZI_ROUTER_T(TX, TW, GG, false); } while (0)
-#define ZI_ROUTER(TX, TW) do { if (grouped) ZI_ROUTER_G(TX, TW, true); else ZI_ROUTER_G(TX, TW, false); } while (0)
+#define ZI_ROUTER(TX, TW) do { if (mode == 2) ZI_ROUTER_G(TX, TW, 2); else if (grouped) ZI_ROUTER_G(TX, TW, 1); else ZI_ROUTER_G(TX, TW, 0); } while (0)
   if (x_dtype == ZI_F32 && w_dtype == ZI_F32) ZI_ROUTER(float, float);
   else if (x_dtype == ZI_F32 && w_dtype == ZI_BF16) ZI_ROUTER(float, bf);
   else if (x_dtype == ZI_BF16 && w_dtype == ZI_F32) ZI_ROUTER(bf, float);
@@ -608,7 +662,7 @@ static int launch_moe_router(int* chosen, float* weight, const void* x, int x_dt
 extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w, int w_dtype,
                              const float* correction, int T, int K, int NR, int top, int renormalize,
                              cudaStream_t stream) {
-  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, false, 0, 1, 1,
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, 0, 0, 1, 1,
                            1.0f, stream);
 }
 
@@ -616,15 +670,33 @@ extern "C" int zi_moe_router(int* chosen, float* weight, const void* x, int x_dt
 extern "C" int zi_moe_router_grouped(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w,
                                      int w_dtype, int T, int K, int NR, int top, int renormalize, int score_kind,
                                      int groups, int keep, float wscale, cudaStream_t stream) {
-  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, nullptr, T, K, NR, top, renormalize, true, score_kind,
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, nullptr, T, K, NR, top, renormalize, 1, score_kind,
                            groups, keep, wscale, stream);
 }
 
 extern "C" int zi_moe_router_grouped_c(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w,
                                        int w_dtype, const float* correction, int T, int K, int NR, int top, int renormalize,
                                        int score_kind, int groups, int keep, float wscale, cudaStream_t stream) {
-  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, true, score_kind,
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, correction, T, K, NR, top, renormalize, 1, score_kind,
                            groups, keep, wscale, stream);
+}
+
+// The router's product, a bias on the logits, the `top` largest logits and the softmax over them alone, in one kernel.
+extern "C" int zi_moe_router_top_logits(int* chosen, float* weight, const void* x, int x_dtype, int ldx, const void* w,
+                                        int w_dtype, const float* bias, int T, int K, int NR, int top, cudaStream_t stream) {
+  return launch_moe_router(chosen, weight, x, x_dtype, ldx, w, w_dtype, bias, T, K, NR, top, 0, 2, 0, 1, 1, 1.0f, stream);
+}
+
+// The same choice from logits already made.
+extern "C" int zi_moe_route_top_logits(int* chosen, float* weight, const float* logits, const float* bias, int T, int NR,
+                                       int top, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || top > NR) return zi_refuse("moe_route: %d of %d outputs cannot be chosen", top, NR);
+  const size_t smem = (size_t)ROUTE_WARPS * NR * sizeof(float);
+  if (smem > 48 * 1024) return zi_refuse("moe_route: %d router outputs are more than this kernel holds", NR);
+  zi_launch(moe_route_top_logits_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, chosen,
+            weight, logits, bias, T, NR, top);
+  return zi_check_launch("moe_route_top_logits");
 }
 
 // Grouped product for tiles of 16 rows (see moe_few_rows_kernel).  x and w of one type (float32 or bfloat16),

@@ -27,13 +27,14 @@ class Run:
     cache: str
     writes: bool
     pre_add: Optional[tuple[str, int]] = None
+    pre_add_input: bool = False
 
 
 def _plan_runs(spec: ModelSpec) -> list[Run]:
     runs, seen = [], set()
     for i, e in enumerate(spec.schedule):
         name = e.cache if e.cache is not None else f"run{i}"
-        runs.append(Run(e.layer, name, writes=name not in seen, pre_add=e.pre_add))
+        runs.append(Run(e.layer, name, writes=name not in seen, pre_add=e.pre_add, pre_add_input=e.pre_add_input))
         seen.add(name)
     return runs
 
@@ -164,8 +165,12 @@ class DecoderModel:
             h = self.embedding.forward(step.token_ids, step, self._embedding_view)
         else:
             h = self.embedding.forward(step.token_ids)
+        # the stream is updated in place: a stack that feeds its input in again keeps a copy of it
+        h0 = h.clone() if any(run.pre_add_input for run in self.runs) else None
         pending = None
         for run, view in zip(self.runs, self._views):
+            if run.pre_add_input:        # one more update that the run's norm adds with the others
+                pending = ops.Several([pending, h0])
             if run.pre_add is None:
                 pending = self.blocks[run.layer].forward(h, pending, step, view)
             else:

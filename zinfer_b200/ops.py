@@ -170,14 +170,28 @@ class Carried:
 
 class Several:
     """Updates of the residual stream that are still to be added, in this order (a block whose sublayers read the
-    same stream leaves one per sublayer): each a tensor, :class:`Partials`, or either inside :class:`Scaled`."""
+    same stream leaves one per sublayer): each a tensor, :class:`Partials`, or either inside :class:`Scaled`.
+    ``row_bias`` (float32 [width]) is a vector that is added to every row with them (an output projection's bias)."""
 
-    def __init__(self, terms):
-        self.terms = [t for t in terms if t is not None]
+    def __init__(self, terms, row_bias: Optional[torch.Tensor] = None):
+        self.terms = []
+        self.row_bias = row_bias
+        for t in terms:
+            if isinstance(t, Several):        # updates that were pending already come first, in their order
+                self.terms += t.terms
+                self.row_bias = _sum_row_bias(t.row_bias, self.row_bias)
+            elif t is not None and not isinstance(t, Carried):
+                self.terms.append(t)
 
     @property
     def shape(self):
         return self.terms[0].shape
+
+
+def _sum_row_bias(a: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if a is None or b is None:
+        return a if b is None else b
+    return a + b
 
 
 def _terms_of(delta) -> list:
@@ -195,7 +209,11 @@ def sum_norm(h: torch.Tensor, delta, w1: torch.Tensor, eps: float, out_dtype: to
     or the pair of norms."""
     T, H = h.shape
     terms = _terms_of(delta)
-    _need(len(terms) <= 4, "at most four updates can be added at once")
+    if isinstance(delta, Several):
+        bias = _sum_row_bias(delta.row_bias, bias)
+    while len(terms) > 4:               # the kernel adds four at once: the first ones go in by themselves, in order
+        _need(rows is None, "more than four updates cannot be added for picked rows")
+        residual_add(h, terms.pop(0))
     _need(h.dtype == torch.float32 and h.is_contiguous(), "the residual stream is contiguous float32")
     for w in (w1, w2):
         _need(w is None or (w.dtype == torch.float32 and w.numel() == H), "norm weights are float32 of the row's width")
@@ -332,6 +350,7 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float,
 
 def residual_add(h: torch.Tensor, delta) -> None:
     if isinstance(delta, Several):
+        _need(delta.row_bias is None, "residual_add: a vector for every row goes in with a norm's kernel")
         for term in delta.terms:
             residual_add(h, term)
         return
@@ -353,17 +372,104 @@ def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
     return x
 
 
-def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x * sigmoid(gate)`` for two [T, width] tensors whose rows may be views of wider rows."""
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None, group: int = 1) -> torch.Tensor:
+    """``x * sigmoid(gate)`` for two [T, width] tensors whose rows may be views of wider rows.  With ``group`` g the
+    gate has width / g columns and each gates g neighbouring columns of ``x`` (a gate per head)."""
     T, W = x.shape
-    _need(gate.shape == x.shape and gate.dtype == x.dtype and x.stride(1) == 1 and gate.stride(1) == 1,
-          "sigmoid_gate: two tensors of one shape and type with dense rows")
+    _need(group >= 1 and W % group == 0 and tuple(gate.shape) == (T, W // group) and gate.dtype == x.dtype
+          and x.stride(1) == 1 and gate.stride(1) == 1,
+          "sigmoid_gate: two tensors of one type with dense rows, the gate with one column per group")
     if out is None:
         out = torch.empty((T, W), dtype=x.dtype, device=x.device)
-    with _prof.region("sigmoid gate", lambda: 3 * T * W * x.element_size()):
-        _check(lib().zi_sigmoid_gate(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _tag(x),
-                                     T, W, _stream()), "sigmoid_gate")
+    with _prof.region("sigmoid gate", lambda: (2 * T * W + T * W // group) * x.element_size()):
+        _check(lib().zi_sigmoid_gate_grouped(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _tag(x),
+                                             T, W, group, _stream()), "sigmoid_gate")
     return out
+
+
+def clamped_gate(gate_up, limit: float, alpha: float, shift: float, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
+    """``g' * sigmoid(alpha * g') * (u' + shift)`` with ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)`` for
+    ``gate_up`` [T, 2I] (gate then up, or interleaved in blocks as :func:`swiglu` has it), a tensor or
+    :class:`Partials` whose splits are added in order."""
+    part = gate_up if isinstance(gate_up, Partials) else None
+    T, two_i = gate_up.shape
+    _need(two_i % 2 == 0, "clamped_gate: gate and up side by side")
+    I = two_i // 2
+    if part is None:
+        _need(gate_up.is_contiguous(), "clamped_gate: a contiguous [T, 2I] tensor")
+    dev = part.data.device if part is not None else gate_up.device
+    out = torch.empty((T, I), dtype=out_dtype, device=dev)
+    src = part.data if part is not None else gate_up
+    with _prof.region("clamped gate", lambda: _nb(out, src)):
+        _check(lib().zi_clamped_gate(_ptr(out), _tag(out), _ptr(None if part is not None else gate_up),
+                                     _tag(gate_up) if part is None else F32, _ptr(part.data if part is not None else None),
+                                     part.splits if part is not None else 0, ctypes.c_longlong(T * two_i), T, I, interleave,
+                                     ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _stream()),
+               "clamped_gate")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm of rows of activations ``x`` [T, n] (a view with dense rows; 32-bit or of ``out_dtype``) times ``weight``."""
+    T, n = x.shape
+    _need(x.stride(1) == 1 and weight.dtype == torch.float32 and weight.numel() == n and weight.is_contiguous(),
+          "rmsnorm_rows: dense rows and a float32 weight of their width")
+    out = torch.empty((T, n), dtype=out_dtype, device=x.device)
+    with _prof.region("rmsnorm of rows", lambda: T * n * (x.element_size() + out.element_size())):
+        _check(lib().zi_rmsnorm_rows(_ptr(out), out.stride(0), _tag(out), _ptr(x), x.stride(0), _tag(x), _ptr(weight),
+                                     ctypes.c_float(eps), T, n, _stream()), "rmsnorm_rows")
+    return out
+
+
+def rope_table_freqs(n_pos: int, freqs: torch.Tensor, magnitude: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin [positions, len(freqs)] of the angles position * freqs[i] (32-bit products), both times ``magnitude``."""
+    _need(freqs.dtype == torch.float32 and freqs.is_contiguous() and freqs.dim() == 1, "frequencies are a float32 vector")
+    half = freqs.numel()
+    cos = torch.empty((n_pos, half), dtype=torch.float32, device=freqs.device)
+    sin = torch.empty_like(cos)
+    _check(lib().zi_rope_table_freqs(_ptr(cos), _ptr(sin), n_pos, half, _ptr(freqs), ctypes.c_float(magnitude), _stream()),
+           "rope_table_freqs")
+    return cos, sin
+
+
+def qkv_rows_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                     value_dim: int, n_gate: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                     eps: float, rot_dims: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                     positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor,
+                     page_size: int, out_dtype: torch.dtype):
+    """What follows a fused projection row [q heads | k heads | v heads | gate columns] when the changes span the whole
+    row: ``bias`` (float32, the row's width) is added; ``q_weight`` / ``k_weight`` (float32 [heads * head_dim] and
+    [kv heads * head_dim]) norm ALL of q and all of k by their root mean square; the first ``rot_dims`` dimensions of
+    every q and k head rotate (pairs (i, i + rot_dims/2)); k and v go into the token's page slot.  ``proj`` may be
+    32-bit beside 16-bit results.  Returns (q [T, heads * head_dim], gate [T, n_gate] or None) in ``out_dtype``."""
+    T = proj.shape[0]
+    qn, kn, vn = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+    width = qn + kn + vn + n_gate
+    _need(proj.stride(1) == 1 and proj.shape[1] == width, "qkv_rows_prepare: rows as wide as their parts")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == width and bias.is_contiguous(), "the bias is float32 of the row's width")
+    for wt, n in ((q_weight, qn), (k_weight, kn)):
+        _need(wt is None or (wt.dtype == torch.float32 and wt.numel() == n and wt.is_contiguous()),
+              "the norms' weights are float32, one value per element of q and of k")
+    n_table = 0
+    if cos is not None:
+        _need(cos.shape == sin.shape and cos.shape[1] == rot_dims // 2 and cos.dtype == torch.float32,
+              "rotary tables are float32 [positions, rot_dims/2]")
+        n_table = cos.shape[0]
+    _need(k_cache.dtype == out_dtype and v_cache.dtype == out_dtype and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          "cache pages have the activations' dtype")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+          and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_dim), "cache pages are [pages, kv heads, page, size]")
+    q = torch.empty((T, qn), dtype=out_dtype, device=proj.device)
+    gate = torch.empty((T, n_gate), dtype=out_dtype, device=proj.device) if n_gate else None
+    with _prof.region("qkv rows (bias, whole norm, rotation, page write)",
+                      lambda: T * width * proj.element_size() + T * width * q.element_size()):
+        _check(lib().zi_qkv_rows_prepare(
+            _ptr(proj), _tag(proj), proj.stride(0), _ptr(bias), _ptr(q), q.stride(0), _ptr(gate), n_gate, n_gate, _tag(q), T,
+            num_heads, num_kv_heads, head_dim, value_dim, _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
+            rot_dims if cos is not None else 0, _ptr(cos), _ptr(sin), n_table, _ptr(_i32(positions, "positions")),
+            _ptr(k_cache), _ptr(v_cache), _ptr(_i32(slots, "slots")), page_size, _stream()), "qkv_rows_prepare")
+    return q, gate
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
@@ -939,6 +1045,33 @@ def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rot_dim: int, rank:
                                        1 if cache is not None else 0, _stream()), "latent_prepare")
 
 
+def latent_prepare_rows(q: torch.Tensor, kv: torch.Tensor, heads: int, dim: int, rot_dim: int, rank: int, rot_dims: int,
+                        neighbours: bool, c_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                        positions: torch.Tensor, q_eff: torch.Tensor, cache: Optional[torch.Tensor],
+                        slots: Optional[torch.Tensor]) -> None:
+    """:func:`latent_prepare` with the queries [T, heads * (dim + rot_dim)] and the rows [T, rank + rot_dim] in tensors
+    (or views) of their own, each 32-bit or of ``q_eff``'s type, and with the rotation's pairs (i, i + rot_dims/2) or, with
+    ``neighbours``, (2i, 2i + 1)."""
+    T = q.shape[0]
+    D = rank + rot_dim
+    _need(q.stride(1) == 1 and q.shape[1] >= heads * (dim + rot_dim) and kv.stride(1) == 1 and kv.shape[1] >= D,
+          "latent_prepare: projection rows")
+    _need(q_eff.is_contiguous() and q_eff.numel() == T * heads * D, "latent_prepare: q_eff")
+    _need(c_weight.dtype == torch.float32 and c_weight.numel() == rank, "latent_prepare: the latent's norm weight")
+    _need(cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rot_dims // 2, "latent_prepare: tables")
+    if cache is not None:
+        _need(cache.is_contiguous() and cache.dtype == q_eff.dtype and cache.shape[-1] == D and cache.shape[1] == 1,
+              "latent_prepare: cache rows")
+        _i32(slots, "slots")
+    with _prof.region("latent prepare", lambda: T * (heads * rot_dim * (q.element_size() + q_eff.element_size())
+                                                     + D * (kv.element_size() + q_eff.element_size()))):
+        _check(lib().zi_latent_prepare_rows(_ptr(q), q.stride(0), _tag(q), _ptr(kv), kv.stride(0), _tag(kv), _tag(q_eff), T, heads,
+                                            dim, rot_dim, rank, rot_dims, 1 if neighbours else 0, _ptr(c_weight),
+                                            ctypes.c_float(eps), _ptr(cos), _ptr(sin), cos.shape[0],
+                                            _ptr(_i32(positions, "positions")), _ptr(q_eff), _ptr(cache), _ptr(slots),
+                                            1 if cache is not None else 0, _stream()), "latent_prepare")
+
+
 # A request that brings this many tokens or more in a bfloat16 step has its latent attention on the
 # tensor cores (two products around a causal softmax); fewer go to the exact kernel.
 LATENT_TENSOR_MIN_TOKENS = 32
@@ -946,7 +1079,8 @@ LATENT_QUERY_BLOCK = 512      # queries per pair of products of a long portion
 
 
 def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, step, heads: int, rank: int,
-                     page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+                     page_size: int, window: Optional[int], scale: float,
+                     sink_logit: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal softmax attention of ``q_eff`` [T, heads * D] over the latent rows of each request's pages
     (``cache`` [pages, 1, page_size, D]): scores over all D columns, values the first ``rank`` columns.
     Returns [T, heads * rank].
@@ -965,7 +1099,9 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
     out = torch.empty((T, heads * rank), dtype=q_eff.dtype, device=q_eff.device)
     skip_from = skip_single = 0
     n_dec = int(getattr(step, "n_dec", 0) or 0)
-    if n_dec > 0 and not window and rank <= 640 and D % 4 == 0 and ATTENTION_BACKEND != "generic":
+    _score_changes_ok(heads, sink_logit, None)
+    plain = not window and sink_logit is None
+    if n_dec > 0 and plain and rank <= 640 and D % 4 == 0 and ATTENTION_BACKEND != "generic":
         # requests that bring one token: split-key kernel, every cached row fetched once for 16 heads
         splits = latent_decode_splits(n_dec, -(-heads // 16), _sm_count(q_eff.device), step.max_kv_len,
                                       fixed=q_eff.dtype == torch.float32)
@@ -982,7 +1118,7 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
         if n_dec == step.n_seqs:
             return out
         skip_single = 1
-    if (q_eff.dtype == torch.bfloat16 and not window and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
+    if (q_eff.dtype == torch.bfloat16 and plain and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
             and D % 8 == 0 and rank % 8 == 0 and getattr(step, "q_lens", None)
             and max(step.q_lens) >= LATENT_TENSOR_MIN_TOKENS):
         skip_from = LATENT_TENSOR_MIN_TOKENS
@@ -995,11 +1131,12 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
         if all(n >= skip_from or (n == 1 and skip_single) for n in step.q_lens):
             return out
     with _prof.region("latent attention (exact, CUDA cores)"):
-        _check(lib().zi_paged_attention_v(
+        _check(lib().zi_paged_attention_mods(
             _ptr(out), out.stride(0), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache), _ptr(cache),
             _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
             _ptr(step.tile_seq), _ptr(step.tile_q0), step.tile_seq.shape[0], heads, 1, D, rank, D, page_size,
-            int(window or 0), ctypes.c_float(scale), skip_from, skip_single, _stream()), "latent_attention")
+            int(window or 0), 0, ctypes.c_float(scale), skip_from, skip_single, ctypes.c_float(0.0), _ptr(sink_logit),
+            ctypes.c_float(0.0), None, 0, _stream()), "latent_attention")
     return out
 
 
@@ -1051,8 +1188,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     cu_q: torch.Tensor, kv_lens: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                     scale: float, out: Optional[torch.Tensor] = None, sink: float = 0.0, keep_first: int = 0,
-                    value_dim: Optional[int] = None) -> torch.Tensor:
-    """Causal attention of the step's query tokens over their requests' pages.  ``sink``: that many keys of
+                    value_dim: Optional[int] = None, sink_logit: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                    dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the step's query tokens over their requests' pages.  Changes to the score, each off unless
+    given: ``softcap`` c (s <- c tanh(s / c) after the scale); ``dist_bias`` (float32 [heads, n]: entry [h, i - j] is
+    added for a key i - j tokens back, distances from n - 1 on share the last entry; neither scaled nor capped);
+    ``sink_logit`` (float32 [heads]: exp(sink_logit[h]) joins head h's denominator and has no value).  ``sink``: that many keys of
     score 0 without a value are counted in the softmax's denominator (p_j = exp(s_j) / (sink + sum exp(s))).
     ``keep_first``: with a window, a request's first tokens that stay visible beyond it (query i sees key j <= i if
     i - j < window or j < keep_first).  ``value_dim``: the values' size where it differs from the keys'.
@@ -1074,13 +1215,24 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _i32(t, name)
     if out is None:
         out = torch.empty((T, num_heads * dv), dtype=q.dtype, device=q.device)
+    _score_changes_ok(num_heads, sink_logit, dist_bias)
     with _prof.region("attention (exact, CUDA cores)"):
-        _check(lib().zi_paged_attention_mask(
+        _check(lib().zi_paged_attention_mods(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), _tag(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
             block_tables.stride(0), _ptr(cu_q), _ptr(kv_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0],
             num_heads, num_kv_heads, head_dim, dv, dv, page_size, int(window or 0), int(keep_first or 0),
-            ctypes.c_float(scale), 0, 0, ctypes.c_float(sink), _stream()), "paged_attention")
+            ctypes.c_float(scale), 0, 0, ctypes.c_float(sink), _ptr(sink_logit), ctypes.c_float(softcap), _ptr(dist_bias),
+            dist_bias.shape[1] if dist_bias is not None else 0, _stream()), "paged_attention")
     return out
+
+
+def _score_changes_ok(num_heads: int, sink_logit: Optional[torch.Tensor], dist_bias: Optional[torch.Tensor]) -> None:
+    if sink_logit is not None:
+        _need(sink_logit.dtype == torch.float32 and sink_logit.numel() == num_heads and sink_logit.is_contiguous(),
+              "a learned sink is float32, one value per query head")
+    if dist_bias is not None:
+        _need(dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and dist_bias.shape[0] == num_heads
+              and dist_bias.is_contiguous(), "a bias by distance is float32 [heads, distances]")
 
 
 ATTENTION_BACKEND = os.environ.get("ZINFER_B200_ATTENTION", "auto")   # auto | generic
@@ -1116,7 +1268,9 @@ def attention_prefill_tile_rows() -> int:
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor, step,
               num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-              scale: float, sink: float = 0.0, keep_first: int = 0, value_dim: Optional[int] = None) -> torch.Tensor:
+              scale: float, sink: float = 0.0, keep_first: int = 0, value_dim: Optional[int] = None,
+              sink_logit: Optional[torch.Tensor] = None, softcap: float = 0.0,
+              dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a step's query tokens over their pages, by the fastest kernel that
     takes the shape: in bfloat16 with head sizes 64/128 (decode also 256) the
     tensor-core kernels (requests that bring one token go to the split-key decode
@@ -1127,14 +1281,17 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     keep_first = int(keep_first or 0) if window else 0
     same_size = value_dim is None or int(value_dim) == head_dim
     # the tensor-core kernels take values of the keys' size; kept first tokens only in the form with a sink
-    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and (not keep_first or bool(sink))
+    changed = sink_logit is not None or softcap or dist_bias is not None
+    fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and (not keep_first or bool(sink)) \
+        and not changed
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if (step.n_dec > 0 and not dec_ok) or (step.n_pf_tiles > 0 and not pf_ok):
         return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
                                num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink,
-                               keep_first=keep_first, value_dim=value_dim)
+                               keep_first=keep_first, value_dim=value_dim, sink_logit=sink_logit, softcap=softcap,
+                               dist_bias=dist_bias)
     _need(q.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: dense operands")
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.dtype == q.dtype,
           "cache pages are [pages, kv heads, page, d] in the activations' dtype")
@@ -1491,6 +1648,29 @@ def moe_router_grouped(x: torch.Tensor, w_router: torch.Tensor, top: int, score:
                                            _tag(w_router), _ptr(correction), T, K, NR, top, 1 if renormalize else 0,
                                            1 if score == "sigmoid" else 0, groups, keep, ctypes.c_float(scale), _stream()),
                "moe_router_grouped")
+    return chosen, weight
+
+
+def moe_router_top_logits(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """The router that chooses by its logits: ``z = x @ w_router^T + bias`` in 32-bit, the ``top`` largest chosen (ties to
+    the lower index), weights = the softmax over the chosen logits alone; product and choice in one kernel.  Rows too
+    long for its shared memory take the CUDA-core product and the choice as two kernels."""
+    T, K = x.shape
+    NR = w_router.shape[0]
+    _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == K, "moe_router: shapes")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == NR and bias.is_contiguous(), "the router's bias is float32, one value per output")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    if K > 32768:
+        logits = linear_cuda_cores(x, w_router, out_dtype=torch.float32)
+        with _prof.region("moe route (largest logits)", lambda: _nb(logits, chosen, weight)):
+            _check(lib().zi_moe_route_top_logits(_ptr(chosen), _ptr(weight), _ptr(logits), _ptr(bias), T, NR, top, _stream()),
+                   "moe_route_top_logits")
+        return chosen, weight
+    with _prof.region(f"moe router (largest logits) N={NR} K={K}", lambda: _nb(w_router) + T * K * x.element_size(), 2 * T * NR * K):
+        _check(lib().zi_moe_router_top_logits(_ptr(chosen), _ptr(weight), _ptr(x), _tag(x), x.stride(0), _ptr(w_router),
+                                              _tag(w_router), _ptr(bias), T, K, NR, top, _stream()), "moe_router_top_logits")
     return chosen, weight
 
 

@@ -18,8 +18,24 @@ window keep a request's first n tokens visible (query i sees key j <= i if i - j
 keep their true positions); ``value_dim`` gives values another size than keys; ``projects_kv: False`` is a mixer
 without key and value projections, which only reads a cache that another layer's run of the same head layout writes
 (with its own queries, window and scale).
+
+Options whose changes span the whole projection row or the score (they switch the mixer to the "rows" form: one
+product [q | k | v | gate] with 32-bit results, one kernel that finishes the row, the attention with the score's
+changes, the gate, the output projection): ``bias`` adds a bias to q, k, v and the output projection (tensors named
+like the matrices plus ``.b``; the output's is handed to the block as ``output_bias`` and joins the residual sum);
+``whole_norm_eps`` norms ALL of q and all of k by their root mean square before the heads are split, with a weight
+per element (``q_norm``, ``k_norm`` of the projections' sizes); ``softcap`` c caps the scaled score, s <- c tanh(s / c);
+``learned_sink`` adds exp(sink[h]) to head h's denominator (tensor ``sink`` [heads]); ``distance_bias`` {rows, far,
+name} adds table[bucket(i - j), h] to the capped score, where the table has ``rows`` rows (None: as many as the file's
+tensor has), bucket(n) = n below rows/2
+and min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) * (rows - rows/2))) from there (the buckets of
+"Exploring the Limits of Transfer Learning with a Unified Text-to-Text Transformer", Raffel et al., 2020, for one
+direction); ``output_gate`` multiplies the heads' outputs by sigmoid(W_g x) before the output projection, ``channel``
+with one gate value per output channel, ``head`` with one per head (tensor ``g``).
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -69,6 +85,33 @@ class GQAttention(Mixer):
         self.general = bool(self.sink or self.values_from_keys or self.keep_first or self.dv != self.d or not self.projects_kv
                             or (self.position is not None and self.rot_dims != self.d and hasattr(self.position, "head_dim")))
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        # ---- the rows form
+        self.has_bias = bool(params.get("bias", False))
+        wn = params.get("whole_norm_eps")
+        self.whole_norm_eps = None if wn is None else float(wn)
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.learned_sink = bool(params.get("learned_sink", False))
+        self.distance_bias = dict(params["distance_bias"]) if params.get("distance_bias") else None
+        self.output_gate = params.get("output_gate")
+        if self.output_gate not in (None, "channel", "head"):
+            raise ValueError(f"an output gate is per channel or per head, not {self.output_gate!r}")
+        self.rows_form = bool(self.has_bias or self.whole_norm_eps is not None or self.softcap or self.learned_sink
+                              or self.distance_bias or self.output_gate)
+        if self.rows_form:
+            if self.qk_norm_eps is not None or self.values_from_keys or self.keep_first or not self.projects_kv or self.sink:
+                raise ValueError("the rows form of attention goes with none of: per-head q/k norm, values from the keys, "
+                                 "kept first tokens, another layer's cache, a counted sink")
+            if getattr(self.position, "pairing", "halves") != "halves":
+                raise ValueError("this mixer rotates pairs (i, i + dims/2) only")
+            if self.distance_bias and not float(self.distance_bias["far"]) > 1.0:
+                raise ValueError(f"a distance table's far end must lie beyond one token, got {self.distance_bias['far']}")
+            self.n_gate = {None: 0, "channel": self.nq * self.dv, "head": self.nq}[self.output_gate]
+            names.setdefault("g", "g")
+            names.setdefault("sink", "sink")
+            if self.whole_norm_eps is not None and "q_norm" not in (params.get("names") or {}):
+                names["q_norm"], names["k_norm"] = names["q"] + ".norm", names["k"] + ".norm"
+        self.output_bias = None
+        self.row_bias = self.sink_logit = self.dist_table = self.w_rows = None
 
     # ------------------------------------------------------------------ weights
     def tensor_specs(self):
@@ -82,6 +125,23 @@ class GQAttention(Mixer):
         if self.qk_norm_eps is not None:
             specs[n["q_norm"]] = TensorSpec((self.d,), init="norm")
             specs[n["k_norm"]] = TensorSpec((self.d,), init="norm")
+        if self.rows_form:
+            if self.has_bias:
+                specs[n["q"] + ".b"] = TensorSpec((q,), init="around_zero")
+                specs[n["k"] + ".b"] = TensorSpec((kv,), init="around_zero")
+                specs[n["v"] + ".b"] = TensorSpec((self.nkv * self.dv,), init="around_zero")
+                specs[n["o"] + ".b"] = TensorSpec((self.hidden,), init="around_zero")
+            if self.whole_norm_eps is not None:
+                specs[n["q_norm"]] = TensorSpec((q,), init="norm")
+                specs[n["k_norm"]] = TensorSpec((kv,), init="norm")
+            if self.learned_sink:
+                specs[n["sink"]] = TensorSpec((self.nq,), init="around_zero")
+            if self.distance_bias:
+                # ``rows`` None: the file gives the number of rows
+                specs[str(self.distance_bias.get("name", "rel"))] = TensorSpec((int(self.distance_bias.get("rows") or -1), self.nq),
+                                                                               init="around_zero", free=32)
+            if self.output_gate:
+                specs[n["g"]] = TensorSpec((self.n_gate, self.hidden))
         return specs
 
     def bind(self, tensors):
@@ -96,6 +156,34 @@ class GQAttention(Mixer):
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[n["q_norm"]].to(torch.float32).contiguous()
             self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
+        if self.rows_form:
+            self._bind_rows(tensors, parts)
+
+    def _bind_rows(self, tensors, parts):
+        n = self.names
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        if self.output_gate:
+            g = tensors[n["g"]]
+            parts = [p.to(torch.float32) for p in parts + [g]] if any(p.dtype != g.dtype for p in parts) else parts + [g]
+        self.w_rows = torch.cat(parts, dim=0).contiguous()        # one product: q, k, v and the gate
+        self.w_qkv = None
+        if self.has_bias:
+            dev = self.w_rows.device
+            self.row_bias = torch.cat([f32(tensors[n[x] + ".b"]) for x in ("q", "k", "v")]
+                                      + [torch.zeros(self.n_gate, dtype=torch.float32, device=dev)]).contiguous()
+            self.output_bias = f32(tensors[n["o"] + ".b"])
+        if self.whole_norm_eps is not None:
+            self.q_norm, self.k_norm = f32(tensors[n["q_norm"]]), f32(tensors[n["k_norm"]])
+        if self.learned_sink:
+            self.sink_logit = f32(tensors[n["sink"]])
+        if self.distance_bias:
+            table = f32(tensors[str(self.distance_bias.get("name", "rel"))])           # [rows, heads]
+            rows, far = int(table.shape[0]), float(self.distance_bias["far"])
+            if rows < 2 or not far > rows // 2:
+                raise ValueError(f"a distance table of {rows} rows needs its far end beyond {rows // 2}, got {far}")
+            buckets = distance_buckets(rows, far)
+            idx = torch.tensor(buckets, dtype=torch.long, device=table.device)
+            self.dist_table = table[idx].transpose(0, 1).contiguous()                    # [heads, distances]
 
     # -------------------------------------------------------------------- cache
     def cache_need(self):
@@ -123,7 +211,26 @@ class GQAttention(Mixer):
                              cache.page_size, self.window, self.scale, sink=self.sink, keep_first=self.keep_first,
                              value_dim=self.dv)
 
+    def _forward_rows(self, x, step, cache):
+        # 32-bit results of the product: the biases and the norm over the whole row meet the unrounded sums
+        proj = ops.linear(x, self.w_rows, out_dtype=torch.float32)
+        group = step.kv_groups[cache.group]
+        cos, sin = self.position.tables() if self.position is not None else (None, None)
+        q, gate = ops.qkv_rows_prepare(proj, self.row_bias, self.nq, self.nkv, self.d, self.dv, self.n_gate, self.q_norm,
+                                       self.k_norm, self.whole_norm_eps or 0.0, self.rot_dims, cos, sin, step.positions,
+                                       cache.k, cache.v, group.slot_mapping, cache.page_size, self.ctx.dtype)
+        heads = ops.attention(q, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d, cache.page_size,
+                              self.window, self.scale, value_dim=self.dv, sink_logit=self.sink_logit, softcap=self.softcap,
+                              dist_bias=self.dist_table)
+        if gate is not None:
+            heads = ops.sigmoid_gate(heads, gate, out=heads, group=self.dv if self.output_gate == "head" else 1)
+        return ops.linear(heads, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
+
     def forward(self, x, step, cache):
+        if self.rows_form:
+            if not cache.writes:
+                raise ValueError("the rows form of attention fills its own cache")
+            return self._forward_rows(x, step, cache)
         if self.general:
             return ops.linear(self.heads_out(x, step, cache), self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
         q_width = self.nq * self.d
@@ -145,3 +252,18 @@ class GQAttention(Mixer):
         o = ops.attention(q, cache.k, cache.v, group.block_tables, step, self.nq, self.nkv, self.d,
                           cache.page_size, self.window, self.scale)
         return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)
+
+
+def distance_buckets(rows: int, far: float) -> list[int]:
+    """Row of a distance table for a key n tokens back, n = 0 .. : one token per row below rows/2, logarithmic steps up
+    to ``far`` from there, the last row beyond; the list ends with the first distance that reaches the last row (every
+    longer distance shares it).  Worked out in 64-bit on the host, once."""
+    half = rows // 2
+    out = []
+    n = 0
+    while True:
+        b = n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b == rows - 1 and n >= half:
+            return out
+        n += 1

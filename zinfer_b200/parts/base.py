@@ -37,7 +37,7 @@ from ..config.spec import PartSpec
 @dataclass(frozen=True)
 class TensorSpec:
     """A tensor a part needs.  ``init`` says how the random-weights mode fills it:
-    ``matrix`` normal(0, 0.02), ``norm`` 1 + U(-0.1, 0.1), ``zeros``; ``integer``
+    ``matrix`` normal(0, 0.02), ``norm`` 1 + U(-0.1, 0.1), ``around_zero`` U(-0.1, 0.1), ``zeros``; ``integer``
     tensors are kept as int32, others in the run's dtype (bfloat16 or float32)
     unless the file stores them in 32-bit, in which case they stay so.
 

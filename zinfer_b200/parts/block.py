@@ -22,7 +22,8 @@ class PreNormBlock(Block):
         self.mixer_norm = make_part(params["mixer_norm"], ctx)
         has_ffn = params.get("feed_forward") is not None
         self.feed_forward = make_part(params["feed_forward"], ctx) if has_ffn else None
-        self.ffn_norm = make_part(params["ffn_norm"], ctx) if has_ffn else None
+        # a block whose sublayers read the same norm's output names no second norm
+        self.ffn_norm = make_part(params["ffn_norm"], ctx) if has_ffn and params.get("ffn_norm") is not None else None
         self.residual_scale = float(params.get("residual_scale", 1.0))
         dot = "" if params.get("verbatim_names") else "."
         self._names = {
@@ -50,8 +51,12 @@ class PreNormBlock(Block):
         return delta if self.residual_scale == 1.0 else ops.Scaled(delta, self.residual_scale)
 
     def forward(self, h, pending, step, cache, bias=None):
+        if self.feed_forward is not None and self.ffn_norm is None:
+            raise ValueError("this arrangement needs a norm before its feed-forward")
         x = self.mixer_norm.forward(h, pending) if bias is None else self.mixer_norm.forward(h, pending, bias=bias)
         a = self._update(self.mixer.forward(x, step, cache))
+        if getattr(self.mixer, "output_bias", None) is not None:
+            a = ops.Several([a], row_bias=self.mixer.output_bias * self.residual_scale)
         if self.feed_forward is None:
             return a
         x = self.ffn_norm.forward(h, a)
@@ -99,14 +104,21 @@ class ParallelBlock(PreNormBlock):
     Both norms share their root mean square, so one kernel makes both from one pass over the stream, and the same
     pass adds what the block before left pending.  The block leaves all its updates pending as :class:`ops.Several`
     (the mixer's output, the feed-forward's, and a shared expert's where the feed-forward hands back a pair): the
-    next block's norm, or the model's last one, adds them, in this order."""
+    next block's norm, or the model's last one, adds them, in this order.  Without ``ffn_norm`` both sublayers read the
+    ONE norm's output, h1 = h + mixer(n) + ffn(n) with n = norm1(h).  A mixer's ``output_bias`` (a vector its output
+    projection adds to every token) goes with the pending updates and is added by the same kernel."""
 
     def forward(self, h, pending, step, cache, bias=None):
-        if self.feed_forward is None:
-            x = ops.sum_norm(h, pending, self.mixer_norm.weight, self.mixer_norm.eps, self.ctx.dtype, bias=bias)
-            return self._update(self.mixer.forward(x, step, cache))
-        x1, x2 = ops.add_rmsnorm_pair(h, pending, self.mixer_norm.weight, self.ffn_norm.weight, self.mixer_norm.eps,
-                                      self.ffn_norm.eps, self.ctx.dtype, bias=bias)
+        row_bias = getattr(self.mixer, "output_bias", None)
+        if row_bias is not None and self.residual_scale != 1.0:
+            row_bias = row_bias * self.residual_scale
+        if self.feed_forward is None or self.ffn_norm is None:
+            x1 = x2 = ops.sum_norm(h, pending, self.mixer_norm.weight, self.mixer_norm.eps, self.ctx.dtype, bias=bias)
+        else:
+            x1, x2 = ops.add_rmsnorm_pair(h, pending, self.mixer_norm.weight, self.ffn_norm.weight, self.mixer_norm.eps,
+                                          self.ffn_norm.eps, self.ctx.dtype, bias=bias)
         a = self.mixer.forward(x1, step, cache)
+        if self.feed_forward is None:
+            return self._update(a) if row_bias is None else ops.Several([self._update(a)], row_bias=row_bias)
         out = self.feed_forward.forward(x2)
-        return ops.Several([self._update(t) for t in (a, *(out if isinstance(out, tuple) else (out,)))])
+        return ops.Several([self._update(t) for t in (a, *(out if isinstance(out, tuple) else (out,)))], row_bias=row_bias)

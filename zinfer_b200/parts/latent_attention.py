@@ -13,7 +13,13 @@ keys only.  The attention runs in the folded form: q_lat,n = W_uk,n^T q_plain,n,
 is [q_lat,n | q_rot,n] . row, the weighted sum runs over the rows' c parts, and W_uv,n is applied
 to that sum: every cached row is read once for all heads, as key and as value.
 
-Rotary positions turn the first ``rot_dims`` of the rot_dim values (pairs (i, i + rot_dims/2)).
+Rotary positions turn the first ``rot_dims`` of the rot_dim values (pairs (i, i + rot_dims/2), or (2i, 2i + 1) when
+the position part says ``pairing: neighbours``).
+
+Options: ``q_rank`` r sends the queries through a latent of their own, q = W_uq norm(W_dq h) (tensors ``dq``,
+``dq.norm``, ``uq`` instead of ``q``; the norm has a plain weight and the layer's eps); ``window`` w lets position i
+see the keys i - w + 1 .. i; ``learned_sink`` adds exp(sink[n]) to head n's softmax denominator (tensor ``sink``
+[heads]; it has no value).
 """
 from __future__ import annotations
 
@@ -39,7 +45,10 @@ class LatentAttention(Mixer):
         self.eps = float(params["norm_eps"])
         self.gated = bool(params.get("output_gate", False))
         self.window = params.get("window")
+        self.q_rank = int(params.get("q_rank") or 0)
+        self.learned_sink = bool(params.get("learned_sink", False))
         self.position = make_part(params["position"], ctx)
+        self.neighbours = getattr(self.position, "pairing", "halves") == "neighbours"
         self.rot_dims = int(getattr(self.position, "head_dim", self.rot_dim))
         if self.rot_dims > self.rot_dim or self.rot_dims % 2:
             raise ValueError(f"{self.rot_dims} rotated dimensions do not fit the rotated part of {self.rot_dim}")
@@ -50,8 +59,12 @@ class LatentAttention(Mixer):
     # ------------------------------------------------------------------ weights
     def tensor_specs(self):
         H, hid = self.heads, self.hidden
+        qw = H * (self.dim + self.rot_dim)
+        queries = {"q": TensorSpec((qw, hid))} if not self.q_rank else {
+            "dq": TensorSpec((self.q_rank, hid)), "dq.norm": TensorSpec((self.q_rank,), init="norm"),
+            "uq": TensorSpec((qw, self.q_rank))}
         specs = {
-            "q": TensorSpec((H * (self.dim + self.rot_dim), hid)),
+            **queries,
             "dkv": TensorSpec((self.row, hid)),
             "dkv.norm": TensorSpec((self.rank,), init="norm"),
             "uk": TensorSpec((H * self.dim, self.rank)),
@@ -60,10 +73,12 @@ class LatentAttention(Mixer):
         }
         if self.gated:
             specs["g"] = TensorSpec((H * self.vdim, hid))
+        if self.learned_sink:
+            specs["sink"] = TensorSpec((H,), init="around_zero")
         return specs
 
     def bind(self, tensors):
-        parts = [tensors["q"], tensors["dkv"]] + ([tensors["g"]] if self.gated else [])
+        parts = [tensors["dq" if self.q_rank else "q"], tensors["dkv"]] + ([tensors["g"]] if self.gated else [])
         if len({p.dtype for p in parts}) > 1:
             parts = [p.to(torch.float32) for p in parts]
         self.w_in = torch.cat(parts, dim=0).contiguous()      # one product: queries, latent, gate
@@ -73,6 +88,10 @@ class LatentAttention(Mixer):
         self.w_uk_t = tensors["uk"].view(H, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = tensors["uv"].view(H, self.vdim, self.rank).contiguous()
         self.w_o = tensors["o"].contiguous()
+        self.sink_logit = tensors["sink"].to(torch.float32).contiguous() if self.learned_sink else None
+        if self.q_rank:
+            self.q_norm = tensors["dq.norm"].to(torch.float32).contiguous()
+            self.w_uq = tensors["uq"].contiguous()
 
     # -------------------------------------------------------------------- cache
     def cache_need(self):
@@ -100,19 +119,37 @@ class LatentAttention(Mixer):
     def forward(self, x, step, cache):
         T, H, D = x.shape[0], self.heads, self.row
         qw = H * (self.dim + self.rot_dim)
-        proj = ops.linear(x, self.w_in, out_dtype=self.ctx.dtype)
         group = step.kv_groups[cache.group]
         cos, sin = self.position.tables()
         q_eff = torch.empty((T, H, D), dtype=self.ctx.dtype, device=x.device)
-        ops.latent_prepare(proj, H, self.dim, self.rot_dim, self.rank, self.rot_dims, self.c_norm, self.eps, cos, sin,
-                           step.positions, q_eff, cache.k if cache.writes else None, group.slot_mapping)
-        q_plain = proj[:, :qw].view(T, H, self.dim + self.rot_dim)[:, :, :self.dim]
+        if self.q_rank:
+            # queries through their own latent: [W_dq; W_dkv; W_g] h with 32-bit results (both norms meet the unrounded
+            # sums), the norm of the query latent, W_uq
+            proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+            qs = ops.linear(ops.rmsnorm_rows(proj[:, :self.q_rank], self.q_norm, self.eps, self.ctx.dtype), self.w_uq,
+                            out_dtype=self.ctx.dtype)
+            ops.latent_prepare_rows(qs, proj[:, self.q_rank:], H, self.dim, self.rot_dim, self.rank, self.rot_dims,
+                                    self.neighbours, self.c_norm, self.eps, cos, sin, step.positions, q_eff,
+                                    cache.k if cache.writes else None, group.slot_mapping)
+            gate_at = self.q_rank + D
+        else:
+            proj = qs = ops.linear(x, self.w_in, out_dtype=self.ctx.dtype)
+            if self.neighbours:
+                ops.latent_prepare_rows(proj, proj[:, qw:], H, self.dim, self.rot_dim, self.rank, self.rot_dims, True,
+                                        self.c_norm, self.eps, cos, sin, step.positions, q_eff,
+                                        cache.k if cache.writes else None, group.slot_mapping)
+            else:
+                ops.latent_prepare(proj, H, self.dim, self.rot_dim, self.rank, self.rot_dims, self.c_norm, self.eps, cos, sin,
+                                   step.positions, q_eff, cache.k if cache.writes else None, group.slot_mapping)
+            gate_at = qw + D
+        q_plain = qs[:, :qw].view(T, H, self.dim + self.rot_dim)[:, :, :self.dim]
         self._per_head(q_plain, self.w_uk_t, q_eff[:, :, :self.rank])
         lat = ops.latent_attention(q_eff.view(T, H * D), cache.k, group.block_tables, step, H, self.rank,
-                                   cache.page_size, self.window, self.scale)
+                                   cache.page_size, self.window, self.scale, sink_logit=self.sink_logit)
         heads = torch.empty((T, H, self.vdim), dtype=self.ctx.dtype, device=x.device)
         self._per_head(lat.view(T, H, self.rank), self.w_uv, heads)
         heads = heads.view(T, H * self.vdim)
         if self.gated:
-            heads = ops.sigmoid_gate(heads, proj[:, qw + D:qw + D + H * self.vdim], out=heads)
+            gate = proj[:, gate_at:gate_at + H * self.vdim]
+            heads = ops.sigmoid_gate(heads, gate if gate.dtype == heads.dtype else gate.to(heads.dtype), out=heads)
         return ops.linear(heads, self.w_o, out_dtype=self.ctx.dtype, allow_partials=True)

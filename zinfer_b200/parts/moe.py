@@ -13,7 +13,9 @@ a ``correction`` is then added to the sigmoid scores for the choice alone, as wi
 largest scores and let only experts of the best groups be chosen; ``weight_scale`` multiplies the weights;
 ``activation: silu_gated`` makes an expert W_down (silu(W_gate h) * (W_up h)); ``shared`` (a feed-forward part) runs
 for every token beside the routed experts, and ``forward`` then hands back the pair (routed, shared) for the block
-to add.
+to add.  ``score: top_logits`` chooses the ``top`` largest logits themselves (``router_bias``: a bias ``router.b`` on the
+logits) and weights them by the softmax over the chosen logits alone.  ``activation: clamped_gated`` makes an expert
+W_down (g' sigmoid(``act_alpha`` g') (u' + 1)) with g' = min(W_gate h, ``limit``) and u' = clamp(W_up h, -limit, limit).
 
 The chosen (token, expert) pairs are laid out by expert on the device, in whole tiles, and two
 grouped products run over them; nothing is read back, so a decode step can be captured.
@@ -37,18 +39,30 @@ class RoutedExperts(FeedForward):
         self.renormalize = bool(params.get("renormalize", False))
         self.has_correction = bool(params.get("correction", False))
         act = params.get("activation", "relu2")
-        if act not in ("relu2", "silu_gated"):
-            raise ValueError(f"experts with activation {act!r} are not built (relu2 and silu_gated are)")
-        self.gated = act == "silu_gated"
+        if act not in ("relu2", "silu_gated", "clamped_gated"):
+            raise ValueError(f"experts with activation {act!r} are not built (relu2, silu_gated and clamped_gated are)")
+        self.gated = act in ("silu_gated", "clamped_gated")
+        self.clamped = act == "clamped_gated"
+        self.limit = float(params.get("limit") or 0.0)
+        self.act_alpha = float(params.get("act_alpha", 1.0))
+        if self.clamped and not self.limit > 0.0:
+            raise ValueError("clamped experts need a positive limit")
         self.score = params.get("score", "softmax")
-        if self.score not in ("softmax", "sigmoid"):
-            raise ValueError(f"router scores are softmax or sigmoid, not {self.score!r}")
+        if self.score not in ("softmax", "sigmoid", "top_logits"):
+            raise ValueError(f"router scores are softmax, sigmoid or top_logits, not {self.score!r}")
+        self.router_bias = bool(params.get("router_bias", False))
+        if self.router_bias and self.score != "top_logits":
+            raise ValueError("a bias on the router's logits is built for the choice by the logits themselves")
         self.groups = int(params.get("groups", 1))
         self.groups_kept = int(params.get("groups_kept", self.groups))
         self.weight_scale = float(params.get("weight_scale", 1.0))
         # the fused router kernel has the softmax over all outputs; everything else takes the general choice
         self.general_route = self.score != "softmax" or self.groups > 1 or self.weight_scale != 1.0
-        if self.general_route:
+        self.top_logits = self.score == "top_logits"
+        if self.top_logits:
+            if self.groups > 1 or self.weight_scale != 1.0 or self.has_correction or self.identity:
+                raise ValueError("the choice by the logits themselves takes no groups, scale, correction or identity experts")
+        elif self.general_route:
             if self.identity:
                 raise ValueError("identity experts are built for the softmax router without groups only")
             if self.groups <= 0 or self.experts % self.groups or not 1 <= self.groups_kept <= self.groups:
@@ -70,6 +84,8 @@ class RoutedExperts(FeedForward):
         specs = {"router": TensorSpec((self.outputs, self.hidden))}
         if self.has_correction:
             specs["correction"] = TensorSpec((self.outputs,), init="zeros")
+        if self.router_bias:
+            specs["router.b"] = TensorSpec((self.outputs,), init="around_zero")
         for e in range(self.experts):
             p = self.expert_names.format(e)
             if self.gated:
@@ -84,6 +100,7 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors):
         self.w_router = tensors["router"].contiguous()
         self.correction = tensors["correction"].to(torch.float32).contiguous() if self.has_correction else None
+        self.bias = tensors["router.b"].to(torch.float32).contiguous() if self.router_bias else None
         ups = [tensors[self.expert_names.format(e) + "up"] for e in range(self.experts)]
         if self.gated:     # an expert's gate rows above its up rows: one product feeds both
             gates = [tensors[self.expert_names.format(e) + self.gate_name] for e in range(self.experts)]
@@ -108,12 +125,16 @@ class RoutedExperts(FeedForward):
 
     def _act(self, mid2):
         """Between an expert's two products, where the first one's kernel has not done it: the gate."""
+        if self.clamped:
+            return ops.clamped_gate(mid2, self.limit, self.act_alpha, 1.0, self.ctx.dtype)
         return ops.swiglu(mid2, out_dtype=self.ctx.dtype, activation="silu") if self.gated else mid2
 
     def routed(self, x):
         T = x.shape[0]
         relu2 = not self.gated
-        if self.general_route and self.hidden <= 32768:
+        if self.top_logits:
+            chosen, weight = ops.moe_router_top_logits(x, self.w_router, self.bias, self.top)
+        elif self.general_route and self.hidden <= 32768:
             chosen, weight = ops.moe_router_grouped(x, self.w_router, self.top, self.score, self.groups, self.groups_kept,
                                                     self.weight_scale, self.renormalize, correction=self.correction)
         elif self.general_route:

@@ -1,6 +1,6 @@
 """Random weights from a configuration and a seed.
 
-Matrices are normal(0, 0.02) and norm weights 1 + U(-0.1, 0.1).  Each tensor has a
+Matrices are normal(0, 0.02), norm weights 1 + U(-0.1, 0.1), and vectors stored around zero U(-0.1, 0.1).  Each tensor has a
 generator of its own, seeded by the seed and the tensor's name, so a tensor's
 values do not depend on which other tensors the model has.  ``write_model_dir``
 writes a model folder (config.json, model.safetensors) that the loader reads back;
@@ -33,6 +33,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, de
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "norm":
         t = 1.0 + (torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32) * 0.2 - 0.1)
+    elif spec.init == "around_zero":     # a norm weight stored around zero (the multiplier is 1 + w), a small bias
+        t = torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32) * 0.2 - 0.1
     elif spec.init == "zeros":
         t = torch.zeros(spec.shape, device=device, dtype=torch.float32)
     else:
