@@ -79,7 +79,8 @@ def cpu_kernels(monkeypatch):
                  "linear_grouped", "linear_grouped_tensor_ok", "moe_router", "linear_few_rows_ok", "gather_rows", "moe_route", "moe_align", "moe_combine", "causal_conv", "rglru_scan", "rglru_decode", "latent_prepare",
                  "latent_attention", "Carried", "norm_residual", "cast_rows", "relu2_", "qk_prepare", "short_conv", "short_conv_carry",
                  "decay_sigmoid_root_", "decay_exp_softplus_", "unit_norm_", "sigmoid_rows", "linear_recurrence", "head_norm_gate",
-                 "moe_route_grouped", "moe_router_grouped", "Several", "sum_norm", "add_rmsnorm_pair", "embed_bigram"):
+                 "moe_route_grouped", "moe_router_grouped", "Several", "sum_norm", "add_rmsnorm_pair", "embed_bigram",
+                 "clamped_gate", "rmsnorm_rows", "rope_table_freqs", "qkv_rows_prepare", "latent_prepare_rows", "moe_router_top_logits"):
         monkeypatch.setattr(ops, name, getattr(kernel_refs, name))
     monkeypatch.setattr(ops, "lib", lambda: None)
     monkeypatch.setattr(runner, "_require_cuda", lambda device: None)

@@ -20,8 +20,15 @@ class Scaled:
 
 
 class Several:
-    def __init__(self, terms):
-        self.terms = [t for t in terms if t is not None]
+    def __init__(self, terms, row_bias=None):
+        self.terms, self.row_bias = [], row_bias
+        for t in terms:
+            if isinstance(t, Several):
+                self.terms += t.terms
+                if t.row_bias is not None:
+                    self.row_bias = t.row_bias if self.row_bias is None else t.row_bias + self.row_bias
+            elif t is not None and type(t).__name__ != "Carried":
+                self.terms.append(t)
 
 
 def _terms_sum(delta):
@@ -39,6 +46,9 @@ def _terms_sum(delta):
 
 
 def sum_norm(h, delta, w1, eps, out_dtype, w2=None, rows=None, bias=None):
+    if isinstance(delta, Several) and delta.row_bias is not None:
+        bias = delta.row_bias if bias is None else delta.row_bias + bias
+        delta = Several(delta.terms)
     x1 = add_rmsnorm(h, _terms_sum(delta), w1, eps, out_dtype, rows=rows, bias=bias)
     if w2 is None:
         return x1
@@ -76,6 +86,8 @@ def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, out=None, bias=None
     if type(delta).__name__ == "Carried":      # nothing pending
         delta = None
     if isinstance(delta, Several):
+        if delta.row_bias is not None:
+            bias = delta.row_bias if bias is None else delta.row_bias + bias
         delta = _terms_sum(delta)
     if isinstance(delta, Scaled):
         delta, scale = delta.delta, delta.scale
@@ -110,8 +122,8 @@ def scale_(x, factor):
     return x
 
 
-def sigmoid_gate(x, gate, out=None):
-    res = (x.to(torch.float32) * torch.sigmoid(gate.to(torch.float32))).to(x.dtype)
+def sigmoid_gate(x, gate, out=None, group=1):
+    res = (x.to(torch.float32) * torch.sigmoid(gate.to(torch.float32)).repeat_interleave(group, dim=1)).to(x.dtype)
     if out is not None:
         out.copy_(res)
         return out
@@ -388,11 +400,11 @@ def latent_decode_splits(n_dec, head_groups, sm_count, max_kv_len, fixed=False):
     return 1
 
 
-def latent_attention(q_eff, cache, block_tables, step, heads, rank, page_size, window, scale):
+def latent_attention(q_eff, cache, block_tables, step, heads, rank, page_size, window, scale, sink_logit=None):
     T = q_eff.shape[0]
     D = cache.shape[-1]
     full = paged_attention(q_eff, cache, cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
-                           heads, 1, D, page_size, window, scale)
+                           heads, 1, D, page_size, window, scale, sink_logit=sink_logit)
     return full.view(T, heads, D)[:, :, :rank].reshape(T, heads * rank).contiguous()
 
 
@@ -405,7 +417,8 @@ def attention_prefill_tile_rows():
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, tile_q0, num_heads, num_kv_heads,
-                    head_dim, page_size, window, scale, out=None, sink=0.0, keep_first=0, value_dim=None):
+                    head_dim, page_size, window, scale, out=None, sink=0.0, keep_first=0, value_dim=None, sink_logit=None,
+                    softcap=0.0, dist_bias=None):
     T = q.shape[0]
     nq, nkv, d = num_heads, num_kv_heads, head_dim
     dv = int(value_dim or d)
@@ -429,7 +442,15 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_q, kv_lens, tile_seq, 
             qt = q[t, :nq * d].to(torch.float32).reshape(nq, d)
             for h in range(nq):
                 sc = (K[:, h // g, :] @ qt[h]) * scale
-                if sink:       # `sink` keys of score 0 without a value
+                if softcap:
+                    sc = softcap * torch.tanh(sc / softcap)
+                if dist_bias is not None:
+                    sc = sc + dist_bias[h, (pos - js).clamp(max=dist_bias.shape[1] - 1)]
+                if sink_logit is not None:       # exp(sink_logit[h]) joins the denominator
+                    m = torch.maximum(sc.max(), sink_logit[h])
+                    e = torch.exp(sc - m)
+                    p = e / (torch.exp(sink_logit[h] - m) + e.sum())
+                elif sink:       # `sink` keys of score 0 without a value
                     e = torch.exp(sc - sc.max())
                     p = e / (sink * torch.exp(-sc.max()) + e.sum())
                 else:
@@ -448,10 +469,10 @@ def linear_argmax(x, weight):
 
 
 def attention(q, k_cache, v_cache, block_tables, step, num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=0.0,
-              keep_first=0, value_dim=None):
+              keep_first=0, value_dim=None, sink_logit=None, softcap=0.0, dist_bias=None):
     return paged_attention(q, k_cache, v_cache, block_tables, step.cu_q, step.kv_lens, step.tile_seq, step.tile_q0,
                            num_heads, num_kv_heads, head_dim, page_size, window, scale, sink=sink, keep_first=keep_first,
-                           value_dim=value_dim)
+                           value_dim=value_dim, sink_logit=sink_logit, softcap=softcap, dist_bias=dist_bias)
 
 
 def patch_tokens(ids, prev, dst, src):
@@ -661,3 +682,85 @@ def moe_route_grouped(logits, top, score="sigmoid", groups=1, keep=1, scale=1.0,
 def moe_router_grouped(x, w_router, top, score="sigmoid", groups=1, keep=1, scale=1.0, renormalize=False, correction=None):
     return moe_route_grouped(x.to(torch.float32) @ w_router.to(torch.float32).T, top, score, groups, keep, scale, renormalize,
                              correction)
+
+
+# ------------------------------------------------ rows of projections, rescaled rotations, clamped gates, logits routers
+def clamped_gate(gate_up, limit, alpha, shift, out_dtype, interleave=0):
+    gu = gate_up.to(torch.float32)
+    I = gu.shape[1] // 2
+    g, u = gu[:, :I].clamp(max=limit), gu[:, I:].clamp(min=-limit, max=limit)
+    return (g * torch.sigmoid(alpha * g) * (u + shift)).to(out_dtype)
+
+
+def rmsnorm_rows(x, weight, eps, out_dtype):
+    v = x.to(torch.float32)
+    return (v * weight * (1.0 / torch.sqrt((v * v).mean(dim=-1, keepdim=True) + torch.tensor(eps, dtype=torch.float32)))).to(out_dtype)
+
+
+def rope_table_freqs(n_pos, freqs, magnitude=1.0):
+    angle = torch.arange(n_pos, dtype=torch.float32, device=freqs.device)[:, None] * freqs[None, :]
+    return ((torch.cos(angle.double()) * magnitude).to(torch.float32), (torch.sin(angle.double()) * magnitude).to(torch.float32))
+
+
+def qkv_rows_prepare(proj, bias, num_heads, num_kv_heads, head_dim, value_dim, n_gate, q_weight, k_weight, eps, rot_dims, cos, sin,
+                     positions, k_cache, v_cache, slots, page_size, out_dtype):
+    T = proj.shape[0]
+    qn, kn, vn = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
+    row = proj.to(torch.float32) + (bias if bias is not None else 0.0)
+    q, k, v, gate = row[:, :qn], row[:, qn:qn + kn], row[:, qn + kn:qn + kn + vn], row[:, qn + kn + vn:]
+
+    def finish(x, w, heads):
+        if w is not None:
+            x = x * w * (1.0 / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + torch.tensor(eps, dtype=torch.float32)))
+        x = x.reshape(T, heads, head_dim)
+        if cos is not None:
+            pos = positions.long()
+            x = _rotate_first(x, cos[pos][:, None, :], sin[pos][:, None, :], rot_dims)
+        return x
+
+    qo = finish(q, q_weight, num_heads).reshape(T, qn).to(out_dtype)
+    ko = finish(k, k_weight, num_kv_heads).to(out_dtype)
+    vo = v.reshape(T, num_kv_heads, value_dim).to(out_dtype)
+    for t in range(T):
+        slot = int(slots[t])
+        if slot >= 0:
+            k_cache[slot // page_size, :, slot % page_size] = ko[t]
+            v_cache[slot // page_size, :, slot % page_size] = vo[t]
+    return qo, (gate.to(out_dtype).contiguous() if n_gate else None)
+
+
+def _rotate_neighbours(v, cos, sin, rot_dims):
+    a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+    turned = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+    return torch.cat([turned, v[..., rot_dims:]], dim=-1)
+
+
+def latent_prepare_rows(q, kv, heads, dim, rot_dim, rank, rot_dims, neighbours, c_weight, eps, cos, sin, positions, q_eff, cache,
+                        slots):
+    T = q.shape[0]
+    D = rank + rot_dim
+    pos = positions.long()
+    c, s = cos[pos], sin[pos]
+    turn = _rotate_neighbours if neighbours else _rotate_first
+    qs = q[:, :heads * (dim + rot_dim)].to(torch.float32).reshape(T, heads, dim + rot_dim)
+    q_eff.view(T, heads, D)[:, :, rank:] = turn(qs[:, :, dim:], c[:, None, :], s[:, None, :], rot_dims).to(q_eff.dtype)
+    if cache is None:
+        return
+    rows = kv[:, :D].to(torch.float32)
+    lat = rows[:, :rank]
+    lat = lat * c_weight * (1.0 / torch.sqrt((lat * lat).mean(dim=-1, keepdim=True) + torch.tensor(eps, dtype=torch.float32)))
+    row = torch.cat([lat, turn(rows[:, rank:], c, s, rot_dims)], dim=-1).to(cache.dtype)
+    page_size = cache.shape[2]
+    for t in range(T):
+        slot = int(slots[t])
+        if slot >= 0:
+            cache[slot // page_size, 0, slot % page_size] = row[t]
+
+
+def moe_router_top_logits(x, w_router, bias, top):
+    z = x.to(torch.float32) @ w_router.to(torch.float32).T
+    if bias is not None:
+        z = z + bias
+    order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
+    weight = torch.softmax(torch.gather(z, 1, order), dim=-1)
+    return order.to(torch.int32), weight
