@@ -137,9 +137,10 @@ class GQAttention(Mixer):
             if self.learned_sink:
                 specs[n["sink"]] = TensorSpec((self.nq,), init="around_zero")
             if self.distance_bias:
-                # ``rows`` None: the file gives the number of rows
+                # ``rows`` None: the file gives the number of rows (random weights: as many as the far end allows, up to 32)
+                free = min(32, max(2, 2 * (math.ceil(float(self.distance_bias["far"])) - 1)))
                 specs[str(self.distance_bias.get("name", "rel"))] = TensorSpec((int(self.distance_bias.get("rows") or -1), self.nq),
-                                                                               init="around_zero", free=32)
+                                                                               init="around_zero", free=free)
             if self.output_gate:
                 specs[n["g"]] = TensorSpec((self.n_gate, self.hidden))
         return specs
