@@ -138,6 +138,17 @@ int zi_paged_attention_mods(void* out, int out_stride, const void* q, int q_stri
                             int d, int dv, int v_row, int page_size, int window, int keep_first, float scale,
                             int skip_from, int skip_single, float sink, const float* sink_logit, float softcap,
                             const float* dist_bias, int n_dist, cudaStream_t stream);
+// The tensor-core kernels (mma.sync, softmax weights as two bfloat16 parts) with the same changes to the score.
+int zi_attention_prefill_mma_mods(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                  const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                  const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv,
+                                  int d, int page_size, int window, float scale, const float* sink_logit, float softcap,
+                                  const float* dist_bias, int n_dist, cudaStream_t stream);
+int zi_attention_decode_mma_mods(void* out, int out_stride, float* workspace, const void* q, int q_stride, const void* kcache,
+                                 const void* vcache, long long n_pages, const int* block_tables, int bt_stride,
+                                 const int* cu_q, const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int d,
+                                 int page_size, int window, float scale, int splits, const float* sink_logit, float softcap,
+                                 const float* dist_bias, int n_dist, cudaStream_t stream);
 // A fused projection row [q heads | k heads | v heads | gate]: biases, an RMS norm over all of q and over all of k
 // (weights per element), rotation of the first rot_dims dimensions of every q and k head, q and the gate columns into
 // tensors of their own, k and v into the token's page slot.  The source may be 32-bit beside 16-bit results.
@@ -221,6 +232,15 @@ int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int 
                       cudaStream_t stream);
 // For a prompt's portion on the tensor cores: a request's cached rows gathered ([kv_pad, D], and the first `rank`
 // columns transposed [rank, kv_pad]), and the causal softmax of the portion's score matrix.
+int zi_latent_decode_mods(void* out, int out_stride, float* work, const void* q, int q_stride, int dtype, const void* cache,
+                          const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens, const int* dec_seq,
+                          int n_dec, int heads, int D, int rank, int page_size, float scale, int splits, int window,
+                          const float* sink_logit, cudaStream_t stream);
+int zi_latent_gather_from(void* keys, void* values_t, const void* cache, int dtype, const int* block_table, int page_size,
+                          int kv_len, int kv_pad, int D, int rank, int kv_start, int kv_first, cudaStream_t stream);
+// Softmax over a block's scores with a window and a learned sink; the weights as two parts, like zi_causal_softmax.
+int zi_window_softmax(void* P, const float* S, int dtype, long long rows, int heads, int pos0, int key0, int n_cols, int window,
+                      float scale, const float* sink_logit, cudaStream_t stream);
 int zi_latent_prepare_rows(const void* q, int ldq, int q_dtype, const void* kv, int ldkv, int kv_dtype, int out_dtype, int T,
                            int heads, int dim, int rd, int rank, int rot_dims, int neighbours, const float* cw, float eps,
                            const float* cos_t, const float* sin_t, int n_table_pos, const int* positions, void* q_eff,

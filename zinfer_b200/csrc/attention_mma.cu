@@ -31,14 +31,15 @@ constexpr int PF_BQ = 128, PF_BK = 64, PF_THREADS = 256;
 // keys of score 0 without a value count in the denominator.
 // With a window, a request's first keep_first keys stay visible (query i sees key j <= i if i - j < window or
 // j < keep_first): the tiles of those keys that lie before the window's first tile are walked first.
-template <int D, bool XP>
+// MD (with XP): the scores are changed as ScoreMods says (a cap, a bias by distance, a learned sink per head).
+template <int D, bool XP, bool MD = false>
 __global__ void __launch_bounds__(PF_THREADS, 2)
 attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_lens, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_q0, int nq, int nkv, int page_size, int page_shift,
-                        int window, float scale_log2, float sink, int keep_first) {
+                        int window, float scale_log2, float sink, int keep_first, const ScoreMods md) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
@@ -154,6 +155,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = s[nt][c] * scale_log2;
+          if constexpr (MD)
+            v = changed_score(md, s[nt][c], h, first_pos + row_lo + (c >> 1) * 8 - (kt + nt * 8 + 2 * (lane & 3) + (c & 1)));
           if (need_mask) {
             const int j = kt + nt * 8 + 2 * (lane & 3) + (c & 1);
             const int pos = first_pos + row_lo + (c >> 1) * 8;
@@ -187,6 +190,9 @@ attn_prefill_mma_kernel(bf16* __restrict__ out, int out_stride, const bf16* __re
     const int r = row_lo + i * 8;
     if (r < nqv) {
       if (XP && sink > 0.f) sum += sink * exp2f(-m[i]);      // the sink's score is 0
+      if constexpr (MD) {
+        if (md.sink_logit) sum += exp2f(md.sink_logit[h] * ZI_LOG2E - m[i]);      // a learned sink of this head
+      }
       const float inv = 1.0f / sum;
       bf16* orow = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D + 2 * (lane & 3);
 #pragma unroll
@@ -201,7 +207,7 @@ struct BlockSync {
   static __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-template <int D, bool FUSED, bool TR, bool TMA, bool XP = false>
+template <int D, bool FUSED, bool TR, bool TMA, bool XP = false, bool MD = false>
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        int* __restrict__ status, bf16* __restrict__ out, int out_stride, float* __restrict__ partial,
@@ -209,7 +215,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const bf16* __restrict__ vcache, const int* __restrict__ block_tables, int bt_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                        const int* __restrict__ dec_seq, int nq, int nkv, int page_size, int page_shift, int window,
-                       float scale_log2, int splits, const FusedQK fq, float sink, int keep_first) {
+                       float scale_log2, int splits, const FusedQK fq, float sink, int keep_first, const ScoreMods md) {
   pdl_launch_dependents();
   // (the unit waits for the kernel before this one itself, after it has asked for its first keys)
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -218,23 +224,23 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   constexpr int RING_BYTES = DC_WARPS * DecodeCfg<D>::STAGES * 2 * DC_KEYS * D * 2;
   constexpr int FUSED_BYTES = FUSED ? 16 * D * 2 + (2 * D + 16) * (int)sizeof(float) : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES + ((FUSED_BYTES + 15) & ~15));
-  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA, XP>(
+  attn_decode_unit<D, FUSED, BlockSync, DecodeCfg<D>::STAGES, TR, TMA, XP, MD>(
       smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, out, out_stride, partial, q, q_stride, kcache, vcache,
       block_tables, bt_stride, cu_q, kv_lens, dec_seq, nq, nkv, page_size, page_shift, window, scale_log2, splits, fq,
-      nullptr, &map_k, &map_v, bars, status, sink, keep_first);
+      nullptr, &map_k, &map_v, bars, status, sink, keep_first, &md);
 }
 
 template <int D>
 __global__ void attn_decode_combine_kernel(bf16* __restrict__ out, int out_stride, const float* __restrict__ partial,
                                            const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int nq,
-                                           int nkv, int splits, float sink) {
+                                           int nkv, int splits, float sink, const float* __restrict__ sink_logit) {
   pdl_launch_dependents();
   // which token this is comes from the step's own arrays (copied before any kernel of the step):
   // these two dependent loads need not wait for the attention kernel
   const int token = cu_q[dec_seq[blockIdx.x]];
   pdl_wait();
   attn_decode_combine_item<D>(blockIdx.x, blockIdx.y, threadIdx.x, blockDim.x, out, out_stride, partial, token, nq, nkv,
-                              splits, sink);
+                              splits, sink, sink_logit);
 }
 
 
@@ -242,8 +248,11 @@ template <int D>
 int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const void* kc, const void* vc,
                    const int* bt, int bt_stride, const int* cu_q, const int* kv_lens, const int* tile_seq,
                    const int* tile_q0, int n_tiles, int nq, int nkv, int page_size, int window, float scale,
-                   cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
-  auto kern = xp ? attn_prefill_mma_kernel<D, true> : attn_prefill_mma_kernel<D, false>;
+                   cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0, const ScoreMods* mods = nullptr) {
+  auto kern = mods ? attn_prefill_mma_kernel<D, true, true> : (xp ? attn_prefill_mma_kernel<D, true> : attn_prefill_mma_kernel<D, false>);
+  ScoreMods md = {};
+  if (mods) md = *mods;
+  md.scale = scale;
   const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * D * 2;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return zi_refuse("attention_prefill: cannot get %zu bytes of shared memory", smem);
@@ -251,7 +260,7 @@ int launch_prefill(void* out, int out_stride, const void* q, int q_stride, const
   zi_launch(kern, dim3(grid), dim3(PF_THREADS), smem, stream, (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)kc,
                                            (const bf16*)vc, bt, bt_stride, cu_q, kv_lens, tile_seq, tile_q0, nq, nkv,
                                            page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, sink,
-                                           keep_first);
+                                           keep_first, md);
   return zi_check_launch("attention_prefill");
 }
 
@@ -259,12 +268,16 @@ int g_decode_transposed = 1;   // zi_attention_decode_transposed(0) switches the
 
 int g_decode_tma = 1;          // see zi_attention_decode_tma
 
-template <int D, bool FUSED, bool TR, bool TMA, bool XP = false>
+template <int D, bool FUSED, bool TR, bool TMA, bool XP = false, bool MD = false>
 int launch_decode_as(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                      const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q,
                      const int* kv_lens, const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window,
-                     float scale, int splits, const FusedQK& fq, cudaStream_t stream, float sink = 0.f, int keep_first = 0) {
-  auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA, XP>;
+                     float scale, int splits, const FusedQK& fq, cudaStream_t stream, float sink = 0.f, int keep_first = 0,
+                     const ScoreMods* mods = nullptr) {
+  auto kern = attn_decode_mma_kernel<D, FUSED, TR, TMA, XP, MD>;
+  ScoreMods md = {};
+  if (mods) md = *mods;
+  md.scale = scale;
   CUtensorMap map_k, map_v;
   memset(&map_k, 0, sizeof(map_k));
   memset(&map_v, 0, sizeof(map_v));
@@ -286,7 +299,7 @@ int launch_decode_as(void* out, int out_stride, float* partial, const void* q, i
   zi_launch(kern, dim3(grid), dim3(DC_THREADS), smem, stream, map_k, map_v, status, (bf16*)out, out_stride,
             splits > 1 ? partial : nullptr, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, bt, bt_stride, cu_q,
             kv_lens, dec_seq, nq, nkv, page_size, log2_or_minus1(page_size), window, scale * 1.4426950408889634f, splits, fq, sink,
-            keep_first);
+            keep_first, md);
   return 0;
 }
 
@@ -294,7 +307,8 @@ template <int D, bool FUSED>
 int launch_decode(void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                   const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                   const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                  const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
+                  const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0,
+                  const ScoreMods* mods = nullptr) {
   // Groups of at most 8 query heads take the transposed tile (keys on the MMA's rows).  Keys and values come by
   // TMA (page boxes, pages of 8, 16, 32, ... tokens whose rows a tensor map can address) while the requests
   // are few, and by cp.async from every lane when they are many.  Measured per 36-layer step (Qwen3-8B
@@ -312,15 +326,22 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
   launch_decode_as<D, false, TR_, TMA_, true>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q,    \
                                               kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, sink, \
                                               keep_first)
+#define ZI_DECODE_MD(TR_, TMA_)                                                                                        \
+  launch_decode_as<D, false, TR_, TMA_, true, true>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, \
+                                                    kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, \
+                                                    sink, keep_first, mods)
   int rc0;
   if constexpr (!FUSED) {
-    if (xp)     // exact weights and a sink: the kernel that only reads q (the fused form makes whole-head rotations)
+    if (mods)   // changed scores (a cap, a bias by distance, a learned sink), exact weights
+      rc0 = tr ? (tma ? ZI_DECODE_MD(true, true) : ZI_DECODE_MD(true, false)) : (tma ? ZI_DECODE_MD(false, true) : ZI_DECODE_MD(false, false));
+    else if (xp)     // exact weights and a sink: the kernel that only reads q (the fused form makes whole-head rotations)
       rc0 = tr ? (tma ? ZI_DECODE_XP(true, true) : ZI_DECODE_XP(true, false)) : (tma ? ZI_DECODE_XP(false, true) : ZI_DECODE_XP(false, false));
     else
       rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false)) : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
   } else {
     rc0 = tr ? (tma ? ZI_DECODE_AS(true, true) : ZI_DECODE_AS(true, false)) : (tma ? ZI_DECODE_AS(false, true) : ZI_DECODE_AS(false, false));
   }
+#undef ZI_DECODE_MD
 #undef ZI_DECODE_XP
 #undef ZI_DECODE_AS
   if (rc0) return rc0;
@@ -328,7 +349,7 @@ int launch_decode(void* out, int out_stride, float* partial, const void* q, int 
   if (rc) return rc;
   if (splits > 1) {
     zi_launch(attn_decode_combine_kernel<D>, dim3(n_dec, nq), dim3(D >= 128 ? 128 : 64), 0, stream, (bf16*)out,
-              out_stride, partial, cu_q, dec_seq, nq, nkv, splits, sink);
+              out_stride, partial, cu_q, dec_seq, nq, nkv, splits, sink, mods ? mods->sink_logit : (const float*)nullptr);
     rc = zi_check_launch("attention_decode_combine");
   }
   return rc;
@@ -338,15 +359,16 @@ template <bool FUSED>
 int dispatch_decode(int d, void* out, int out_stride, float* partial, const void* q, int q_stride, const void* kc,
                     const void* vc, long long n_pages, const int* bt, int bt_stride, const int* cu_q, const int* kv_lens,
                     const int* dec_seq, int n_dec, int nq, int nkv, int page_size, int window, float scale, int splits,
-                    const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0) {
+                    const FusedQK& fq, cudaStream_t stream, bool xp = false, float sink = 0.f, int keep_first = 0,
+                    const ScoreMods* mods = nullptr) {
   if (d == 64)
     return launch_decode<64, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
+                                    n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first, mods);
   if (d == 128)
     return launch_decode<128, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens,
-                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
+                                     dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first, mods);
   return launch_decode<256, FUSED>(out, out_stride, partial, q, q_stride, kc, vc, n_pages, bt, bt_stride, cu_q, kv_lens, dec_seq,
-                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first);
+                                   n_dec, nq, nkv, page_size, window, scale, splits, fq, stream, xp, sink, keep_first, mods);
 }
 }  // namespace
 
@@ -417,6 +439,44 @@ extern "C" int zi_attention_prefill_mma_mask(void* out, int out_stride, const vo
                               tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink, keep_first);
   return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, sink, keep_first);
+}
+
+// The same with changed scores: softcap c (s <- c tanh(s / c)), dist_bias [heads][n_dist] (added by the distance between
+// query and key), sink_logit [heads] (exp of it joins the head's denominator); each off when 0 or null.
+extern "C" int zi_attention_prefill_mma_mods(void* out, int out_stride, const void* q, int q_stride, const void* kcache,
+                                             const void* vcache, const int* block_tables, int bt_stride, const int* cu_q,
+                                             const int* kv_lens, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                             int nq, int nkv, int d, int page_size, int window, float scale,
+                                             const float* sink_logit, float softcap, const float* dist_bias, int n_dist,
+                                             cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 0)) return zi_refuse("attention_prefill: head_dim %d is not 64 or 128", d);
+  if (q_stride % 8 || ((uintptr_t)q % 16)) return zi_refuse("attention_prefill: q rows must be 16-byte aligned");
+  if (!(softcap >= 0.f) || (dist_bias && n_dist <= 0)) return zi_refuse("attention_prefill: a cap below zero or an empty distance table");
+  ScoreMods md = {sink_logit, dist_bias, n_dist, softcap, scale};
+  if (d == 64)
+    return launch_prefill<64>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                              tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, 0.f, 0, &md);
+  return launch_prefill<128>(out, out_stride, q, q_stride, kcache, vcache, block_tables, bt_stride, cu_q, kv_lens,
+                             tile_seq, tile_q0, n_tiles, nq, nkv, page_size, window, scale, stream, true, 0.f, 0, &md);
+}
+
+extern "C" int zi_attention_decode_mma_mods(void* out, int out_stride, float* workspace, const void* q, int q_stride,
+                                            const void* kcache, const void* vcache, long long n_pages,
+                                            const int* block_tables, int bt_stride, const int* cu_q, const int* kv_lens,
+                                            const int* dec_seq, int n_dec, int nq, int nkv, int d, int page_size,
+                                            int window, float scale, int splits, const float* sink_logit, float softcap,
+                                            const float* dist_bias, int n_dist, cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (!zi_attention_mma_supported(nq, nkv, d, 1))
+    return zi_refuse("attention_decode: head_dim %d (64, 128, 256) or group size %d (<= 16) is not supported", d, nq / nkv);
+  if (splits < 1 || (splits > 1 && !workspace)) return zi_refuse("attention_decode: %d splits need a workspace", splits);
+  if (q_stride % 2) return zi_refuse("attention_decode: q rows must be 4-byte aligned");
+  if (!(softcap >= 0.f) || (dist_bias && n_dist <= 0)) return zi_refuse("attention_decode: a cap below zero or an empty distance table");
+  FusedQK none = {};
+  ScoreMods md = {sink_logit, dist_bias, n_dist, softcap, scale};
+  return dispatch_decode<false>(d, out, out_stride, workspace, q, q_stride, kcache, vcache, n_pages, block_tables, bt_stride, cu_q,
+                                kv_lens, dec_seq, n_dec, nq, nkv, page_size, window, scale, splits, none, stream, true, 0.f, 0, &md);
 }
 
 extern "C" int zi_attention_decode_mma_sink(void* out, int out_stride, float* workspace, const void* q, int q_stride,

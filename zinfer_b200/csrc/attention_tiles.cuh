@@ -305,6 +305,25 @@ __device__ __forceinline__ void tma_kv_tile(uint8_t* ks, uint8_t* vs, uint64_t* 
 // ================================================================================ decode
 constexpr int DC_THREADS = 128, DC_WARPS = 4, DC_KEYS = 16, DC_TILE = DC_WARPS * DC_KEYS;
 // stages of a warp's private ring: 3 x 8 KB x 4 warps = 96 KB per CTA at d = 128, two CTAs per SM
+// Changes to a score (the form MD of the kernels below): s <- scale * (q . k); with softcap c > 0, s <- c tanh(s / c);
+// with dist_bias [heads][n_dist], s += dist_bias[head][min(i - j, n_dist - 1)] (neither scaled nor capped); with
+// sink_logit [heads], exp(sink_logit[head]) joins the head's denominator (no value).  `scale` is the plain scale (the
+// kernels' scale_log2 is unused in this form).
+struct ScoreMods {
+  const float* sink_logit;
+  const float* dist_bias;
+  int n_dist;
+  float softcap;
+  float scale;
+};
+constexpr float ZI_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float changed_score(const ScoreMods& md, float dot, int head, int dist) {
+  float v = dot * md.scale;
+  if (md.softcap > 0.f) v = md.softcap * tanhf(v / md.softcap);
+  if (md.dist_bias) v += md.dist_bias[(size_t)head * md.n_dist + min(max(dist, 0), md.n_dist - 1)];
+  return v * ZI_LOG2E;
+}
+
 template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2); };
 
 // What the fused form needs to make q, k and v of the step's token itself from the fused
@@ -348,7 +367,9 @@ struct FusedQK {
 // a code in `status`; else by cp.async from every lane.
 // XP: the softmax weights meet the values as two bfloat16 parts (high and rest), and `sink` keys of score 0
 // without a value count in the denominator (where the unit itself divides; else the kernel that combines the splits does).
-template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false, bool TMA = false, bool XP = false>
+// MD (with XP): the scores are changed as ScoreMods says.
+template <int D, bool FUSED, class Sync, int STAGES = DecodeCfg<D>::STAGES, bool TR = false, bool TMA = false, bool XP = false,
+          bool MD = false>
 __device__ __forceinline__ void attn_decode_unit(
     uint8_t* smem, int tid, int dec, int kvh, int z, bf16* __restrict__ out, int out_stride,
     float* __restrict__ partial, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
@@ -356,7 +377,7 @@ __device__ __forceinline__ void attn_decode_unit(
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq, int nq, int nkv,
     int page_size, int page_shift, int window, float scale_log2, int splits, const FusedQK& fq,
     uint8_t* fused_area = nullptr, const CUtensorMap* map_k = nullptr, const CUtensorMap* map_v = nullptr,
-    uint64_t* bars = nullptr, int* status = nullptr, float sink = 0.f, int keep_first = 0) {
+    uint64_t* bars = nullptr, int* status = nullptr, float sink = 0.f, int keep_first = 0, const ScoreMods* md = nullptr) {
 
   constexpr int ROWS_BYTES = DC_KEYS * D * 2;                  // one warp's 16 keys of K (or V)
   constexpr int WARP_BYTES = STAGES * 2 * ROWS_BYTES;          // a warp's private ring
@@ -653,6 +674,10 @@ __device__ __forceinline__ void attn_decode_unit(
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = st[c] * scale_log2;
+          if constexpr (MD) {
+            const int j = key0 + (lane >> 2) + (c >> 1) * 8;
+            v = changed_score(*md, st[c], kvh * g + min(2 * (lane & 3) + (c & 1), g - 1), pos - j);
+          }
           if (need_mask) {
             const int j = key0 + (lane >> 2) + (c >> 1) * 8;
             if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;
@@ -703,6 +728,10 @@ __device__ __forceinline__ void attn_decode_unit(
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = s[nt][c] * scale_log2;
+          if constexpr (MD) {
+            const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
+            v = changed_score(*md, s[nt][c], kvh * g + min((lane >> 2) + (c >> 1) * 8, g - 1), pos - j);
+          }
           if (need_mask) {
             const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
             if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;
@@ -800,6 +829,9 @@ __device__ __forceinline__ void attn_decode_unit(
       }
     } else {
       if (XP && sink > 0.f) lt += sink * exp2f(-mt);      // the sink's score is 0
+      if constexpr (MD) {
+        if (md->sink_logit) lt += exp2f(md->sink_logit[kvh * g + r] * ZI_LOG2E - mt);      // a learned sink
+      }
       out[(size_t)token * out_stride + (size_t)(kvh * g + r) * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
     }
   }
@@ -810,7 +842,8 @@ __device__ __forceinline__ void attn_decode_unit(
 template <int D>
 __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid, int nthreads, bf16* __restrict__ out,
                                                          int out_stride, const float* partial, int token, int nq,
-                                                         int nkv, int splits, float sink = 0.f) {
+                                                         int nkv, int splits, float sink = 0.f,
+                                                         const float* sink_logit = nullptr) {
   const int g = nq / nkv, kvh = h / g, r = h % g;
   const float* base = partial + ((((size_t)dec * nkv + kvh) * splits) * g + r) * (D + 2);
   const size_t zstride = (size_t)g * (D + 2);
@@ -827,6 +860,7 @@ __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid
     float lt = 0.f;
     for (int z = 0; z < splits; ++z) lt += __shfl_sync(0xffffffffu, lz * sc, z);   // in split order
     if (sink > 0.f) lt += sink * exp2f(-mt);      // a sink: keys of score 0 without a value, in the denominator only
+    if (sink_logit) lt += exp2f(sink_logit[h] * 1.4426950408889634f - mt);      // a learned sink of this head
     for (int c = tid; c < D; c += nthreads) {   // whole warps run this loop together (D is a multiple of nthreads or the reverse)
       float acc = 0.f;
       for (int z0 = 0; z0 < splits; z0 += 8) {
@@ -851,6 +885,7 @@ __device__ __forceinline__ void attn_decode_combine_item(int dec, int h, int tid
       lt += base[z * zstride + D + 1] * sc;
     }
     if (sink > 0.f) lt += sink * exp2f(-mt);
+    if (sink_logit) lt += exp2f(sink_logit[h] * 1.4426950408889634f - mt);
     out[(size_t)token * out_stride + (size_t)h * D + c] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
   }
 }

@@ -82,18 +82,21 @@ latent_prepare_kernel(const TQ* __restrict__ qsrc, int ldq, const TS* __restrict
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_gather_kernel(T* __restrict__ keys, T* __restrict__ values_t, const T* __restrict__ cache,
-                     const int* __restrict__ block_table, int page_size, int kv_len, int kv_pad, int D, int rank) {
+                     const int* __restrict__ block_table, int page_size, int kv_len, int kv_pad, int D, int rank,
+                     int kv_start, int kv_first) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char raw[];
   T* tile = reinterpret_cast<T*>(raw);           // [32][D + 2]
+  // row j of the outputs is the key at position kv_start + j; positions before kv_first (behind every window) are zero
   const int j0 = blockIdx.x * 32, pitch = D + 2;
   for (int e = threadIdx.x; e < 32 * D; e += blockDim.x) {
     const int kk = e / D, c = e - kk * D, j = j0 + kk;
     T v = from_f32<T>(0.f);
-    if (j < kv_len) {
-      const int page = block_table[j / page_size];
-      if (page >= 0) v = cache[((size_t)page * page_size + (j % page_size)) * D + c];
+    if (j < kv_len && kv_start + j >= kv_first) {
+      const int at = kv_start + j;
+      const int page = block_table[at / page_size];
+      if (page >= 0) v = cache[((size_t)page * page_size + (at % page_size)) * D + c];
     }
     tile[kk * pitch + c] = v;
     if (j < kv_pad) keys[(size_t)j * D + c] = v;
@@ -144,6 +147,46 @@ causal_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads,
   }
 }
 
+// The same with a window and a learned sink: column j of S is the key at position key0 + j; the query of row (t, h) at
+// position pos0 + t sees the keys max(0, pos - window + 1) .. pos (window 0: all up to pos); exp(sink_logit[h]) joins
+// the denominator (null: none).
+template <typename T>
+__global__ void __launch_bounds__(256)
+window_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int heads, int pos0, int key0, int n_cols, int window,
+                      float scale, const float* __restrict__ sink_logit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  __shared__ float red[8];
+  const size_t row = blockIdx.x;
+  const int pos = pos0 + (int)(row / heads), h = (int)(row % heads);
+  const int lo = max(0, (window > 0 ? max(0, pos - window + 1) : 0) - key0), hi = min(n_cols, pos - key0 + 1);
+  const float* s = S + row * n_cols;
+  T* p = P + row * 2 * n_cols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float m = -INFINITY;
+  for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) m = fmaxf(m, s[j]);
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+  m *= scale;
+  if (sink_logit) m = fmaxf(m, sink_logit[h]);
+  float sum = 0.f;
+  for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) sum += expf(scale * s[j] - m);
+  sum = block_sum(sum, scratch);
+  if (sink_logit) sum += expf(sink_logit[h] - m);
+  const float inv = 1.0f / sum;
+  for (int j = threadIdx.x; j < n_cols; j += blockDim.x) {
+    const float w = j >= lo && j < hi ? expf(scale * s[j] - m) * inv : 0.f;
+    const T hi_part = from_f32<T>(w);
+    p[2 * j] = hi_part;
+    p[2 * j + 1] = from_f32<T>(w - to_f32(hi_part));
+  }
+}
+
 // ------------------------------------------------------------ single tokens: split-key decode
 // A request that brings one token: its `heads` query rows [D] against its kv_len cached rows, which
 // every head shares.  Block (key split, request, group of 16 heads): 256 threads walk the split's keys
@@ -161,7 +204,8 @@ __global__ void __launch_bounds__(LD_THREADS)
 latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ work, const T* __restrict__ q, int q_stride,
                      const T* __restrict__ cache, const int* __restrict__ block_tables, int bt_stride,
                      const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const int* __restrict__ dec_seq,
-                     int heads, int D, int rank, int page_size, float scale, int splits) {
+                     int heads, int D, int rank, int page_size, float scale, int splits, int window,
+                     const float* __restrict__ sink_logit) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -176,10 +220,12 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* bt = block_tables + (size_t)seq * bt_stride;
   const bool vec8 = sizeof(T) == 2 && D % 8 == 0 && ((uintptr_t)cache & 15) == 0;
-  // this split's keys: whole tiles, dealt out evenly
-  const int tiles = (kv_len + LD_KEYS - 1) / LD_KEYS;
+  // this split's keys: whole tiles, dealt out evenly; with a window the token sees its last `window` keys only
+  const int kv_begin = window > 0 ? max(0, kv_len - window) : 0;
+  const int first_tile = kv_begin / LD_KEYS;
+  const int tiles = (kv_len + LD_KEYS - 1) / LD_KEYS - first_tile;
   const int per = (tiles + splits - 1) / splits;
-  const int t_begin = split * per, t_end = min(tiles, t_begin + per);
+  const int t_begin = first_tile + split * per, t_end = min(first_tile + tiles, t_begin + per);
 
   for (int h = warp; h < LD_HEADS; h += LD_THREADS / 32) {       // a warp per query row
     const T* qr = q + (size_t)tok * q_stride + (size_t)(h0 + h) * D;
@@ -199,7 +245,7 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
     __syncthreads();     // the tile before is consumed (the first time: qs is written)
     for (int kk = warp; kk < LD_KEYS; kk += LD_THREADS / 32) {      // a warp per cached row: one page lookup
       const int j = k0 + kk;
-      const int page = j < kv_len ? bt[j / page_size] : -1;
+      const int page = j < kv_len && j >= kv_begin ? bt[j / page_size] : -1;     // (pages behind the window may be gone)
       float* dst = ks + kk * KP;
       if (page < 0) {
         for (int c = lane; c < D; c += 32) dst[c] = 0.f;
@@ -229,7 +275,7 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
         sb = fmaf(b4.x, kv.x, fmaf(b4.y, kv.y, fmaf(b4.z, kv.z, fmaf(b4.w, kv.w, sb))));
       }
     }
-    const bool live = k0 + lane < kv_len;
+    const bool live = k0 + lane < kv_len && k0 + lane >= kv_begin;
     sa = live ? sa * scale : -INFINITY;
     sb = live ? sb * scale : -INFINITY;
     const float na = fmaxf(m_a, warp_max(sa)), nb = fmaxf(m_b, warp_max(sb));    // finite: a tile has a live key
@@ -279,7 +325,8 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
     if (h >= nh) continue;
     const float mh = ps[h], lh = ps[LD_HEADS + h];
     if (splits == 1) {
-      const float inv = 1.0f / lh;
+      // a learned sink: exp(sink_logit[head]) in the denominator, without a value
+      const float inv = 1.0f / (sink_logit ? lh + expf(sink_logit[h0 + h] - mh) : lh);
       T* o = out + (size_t)tok * out_stride + (size_t)(h0 + h) * rank;
 #pragma unroll
       for (int j = 0; j < LD_MAXC; ++j)
@@ -301,7 +348,7 @@ latent_decode_kernel(T* __restrict__ out, int out_stride, float* __restrict__ wo
 template <typename T>
 __global__ void latent_decode_merge_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ work,
                                            const int* __restrict__ cu_q, const int* __restrict__ dec_seq, int heads,
-                                           int rank, int splits) {
+                                           int rank, int splits, const float* __restrict__ sink_logit) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
@@ -312,6 +359,7 @@ __global__ void latent_decode_merge_kernel(T* __restrict__ out, int out_stride, 
   for (int s = 0; s < splits; ++s) m = fmaxf(m, w[s * stride]);
   float l = 0.f;
   for (int s = 0; s < splits; ++s) l += w[s * stride + 1] * expf(w[s * stride] - m);
+  if (sink_logit) l += expf(sink_logit[h] - m);
   const float inv = 1.0f / l;
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float o = 0.f;
@@ -329,7 +377,19 @@ extern "C" int zi_latent_decode(void* out, int out_stride, float* work, const vo
                                 const void* cache, const int* block_tables, int bt_stride, const int* cu_q,
                                 const int* kv_lens, const int* dec_seq, int n_dec, int heads, int D, int rank,
                                 int page_size, float scale, int splits, cudaStream_t stream) {
+  return zi_latent_decode_mods(out, out_stride, work, q, q_stride, dtype, cache, block_tables, bt_stride, cu_q, kv_lens, dec_seq,
+                               n_dec, heads, D, rank, page_size, scale, splits, 0, nullptr, stream);
+}
+
+// The same with a window (a token sees its last `window` keys; 0: all) and a learned sink per head (sink_logit [heads],
+// exp of it in the denominator; null: none).
+extern "C" int zi_latent_decode_mods(void* out, int out_stride, float* work, const void* q, int q_stride, int dtype,
+                                     const void* cache, const int* block_tables, int bt_stride, const int* cu_q,
+                                     const int* kv_lens, const int* dec_seq, int n_dec, int heads, int D, int rank,
+                                     int page_size, float scale, int splits, int window, const float* sink_logit,
+                                     cudaStream_t stream) {
   if (n_dec <= 0) return 0;
+  if (window < 0) return zi_refuse("latent_decode: a window of %d keys", window);
   if (rank > 128 * LD_MAXC || rank > D) return zi_refuse("latent_decode: a latent of %d values (rows of %d) is more than this kernel holds", rank, D);
   if (splits < 1 || (splits > 1 && !work)) return zi_refuse("latent_decode: %d splits need a workspace", splits);
   if (D % 4) return zi_refuse("latent_decode: rows of %d values are not whole 16-byte pieces", D);
@@ -340,17 +400,26 @@ extern "C" int zi_latent_decode(void* out, int out_stride, float* work, const vo
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return zi_refuse("latent_decode: cannot get %zu bytes of shared memory", smem);
     zi_launch(kern, dim3(grid), dim3(LD_THREADS), smem, stream, (TT*)out, out_stride, work, (const TT*)q, q_stride,
-              (const TT*)cache, block_tables, bt_stride, cu_q, kv_lens, dec_seq, heads, D, rank, page_size, scale, splits);
+              (const TT*)cache, block_tables, bt_stride, cu_q, kv_lens, dec_seq, heads, D, rank, page_size, scale, splits, window,
+              sink_logit);
     if (splits > 1)
       zi_launch(latent_decode_merge_kernel<TT>, dim3(n_dec, heads), dim3(128), 0, stream, (TT*)out, out_stride,
-                (const float*)work, cu_q, dec_seq, heads, rank, splits);
+                (const float*)work, cu_q, dec_seq, heads, rank, splits, sink_logit);
   });
   return zi_check_launch("latent_decode");
 }
 
 extern "C" int zi_latent_gather(void* keys, void* values_t, const void* cache, int dtype, const int* block_table,
                                 int page_size, int kv_len, int kv_pad, int D, int rank, cudaStream_t stream) {
+  return zi_latent_gather_from(keys, values_t, cache, dtype, block_table, page_size, kv_len, kv_pad, D, rank, 0, 0, stream);
+}
+
+// The same for the kv_len keys from position kv_start on; positions before kv_first are left zero (their pages may be gone).
+extern "C" int zi_latent_gather_from(void* keys, void* values_t, const void* cache, int dtype, const int* block_table,
+                                     int page_size, int kv_len, int kv_pad, int D, int rank, int kv_start, int kv_first,
+                                     cudaStream_t stream) {
   if (kv_pad <= 0) return 0;
+  if (kv_start < 0) return zi_refuse("latent_gather: keys from position %d", kv_start);
   if (rank > D || kv_len > kv_pad) return zi_refuse("latent_gather: rank %d of %d columns, %d of %d keys", rank, D, kv_len, kv_pad);
   const size_t smem = (size_t)32 * (D + 2) * (dtype == ZI_F32 ? 4 : 2);
   ZI_DISPATCH_DTYPE(dtype, TT, {
@@ -358,7 +427,7 @@ extern "C" int zi_latent_gather(void* keys, void* values_t, const void* cache, i
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return zi_refuse("latent_gather: cannot get %zu bytes of shared memory", smem);
     zi_launch(kern, dim3((kv_pad + 31) / 32), dim3(256), smem, stream, (TT*)keys, (TT*)values_t, (const TT*)cache,
-              block_table, page_size, kv_len, kv_pad, D, rank);
+              block_table, page_size, kv_len, kv_pad, D, rank, kv_start, kv_first);
   });
   return zi_check_launch("latent_gather");
 }
@@ -370,6 +439,16 @@ extern "C" int zi_causal_softmax(void* P, const float* S, int dtype, long long r
   ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(causal_softmax_kernel<TT>, dim3((unsigned)rows), dim3(256), 0, stream, (TT*)P, S,
                                          heads, ctx, kv_pad, scale));
   return zi_check_launch("causal_softmax");
+}
+
+extern "C" int zi_window_softmax(void* P, const float* S, int dtype, long long rows, int heads, int pos0, int key0, int n_cols,
+                                 int window, float scale, const float* sink_logit, cudaStream_t stream) {
+  if (rows <= 0 || n_cols <= 0) return 0;
+  if (rows > 0x7fffffffLL) return zi_refuse("window_softmax: too many rows");
+  if (!(scale > 0.f)) return zi_refuse("window_softmax: the scale must be positive");
+  ZI_DISPATCH_DTYPE(dtype, TT, zi_launch(window_softmax_kernel<TT>, dim3((unsigned)rows), dim3(256), 0, stream, (TT*)P, S,
+                                         heads, pos0, key0, n_cols, window, scale, sink_logit));
+  return zi_check_launch("window_softmax");
 }
 
 extern "C" int zi_latent_prepare(const void* src, int ld, int dtype, int T, int heads, int dim, int rd, int rank,

@@ -1100,25 +1100,27 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
     skip_from = skip_single = 0
     n_dec = int(getattr(step, "n_dec", 0) or 0)
     _score_changes_ok(heads, sink_logit, None)
-    plain = not window and sink_logit is None
-    if n_dec > 0 and plain and rank <= 640 and D % 4 == 0 and ATTENTION_BACKEND != "generic":
+    win = int(window or 0)
+    if n_dec > 0 and rank <= 640 and D % 4 == 0 and ATTENTION_BACKEND != "generic":
         # requests that bring one token: split-key kernel, every cached row fetched once for 16 heads
-        splits = latent_decode_splits(n_dec, -(-heads // 16), _sm_count(q_eff.device), step.max_kv_len,
+        longest = step.max_kv_len if not win else min(step.max_kv_len or win, win)
+        splits = latent_decode_splits(n_dec, -(-heads // 16), _sm_count(q_eff.device), longest,
                                       fixed=q_eff.dtype == torch.float32)
         need = lib().zi_latent_decode_workspace_floats(n_dec, heads, rank, splits)
         ws = torch.empty((need,), dtype=torch.float32, device=q_eff.device) if need else None
+        seen = lambda c: min(c + 1, win) if win else c + 1
         with _prof.region("latent attention (decode, split keys)",
-                          lambda: sum((c + 1) * D for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1) * q_eff.element_size(),
-                          sum(2 * heads * (c + 1) * (D + rank) for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1)):
-            _check(lib().zi_latent_decode(
+                          lambda: sum(seen(c) * D for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1) * q_eff.element_size(),
+                          sum(2 * heads * seen(c) * (D + rank) for q_, c in zip(step.q_lens, step.ctx_lens) if q_ == 1)):
+            _check(lib().zi_latent_decode_mods(
                 _ptr(out), out.stride(0), _ptr(ws), _ptr(q_eff), q_eff.stride(0), _tag(q_eff), _ptr(cache),
                 _ptr(_i32(block_tables, "block_tables")), block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens),
-                _ptr(step.dec_seq), n_dec, heads, D, rank, page_size, ctypes.c_float(scale), splits, _stream()),
-                "latent_decode")
+                _ptr(step.dec_seq), n_dec, heads, D, rank, page_size, ctypes.c_float(scale), splits, win, _ptr(sink_logit),
+                _stream()), "latent_decode")
         if n_dec == step.n_seqs:
             return out
         skip_single = 1
-    if (q_eff.dtype == torch.bfloat16 and plain and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
+    if (q_eff.dtype == torch.bfloat16 and GEMM_BACKEND != "simt" and ATTENTION_BACKEND != "generic"
             and D % 8 == 0 and rank % 8 == 0 and getattr(step, "q_lens", None)
             and max(step.q_lens) >= LATENT_TENSOR_MIN_TOKENS):
         skip_from = LATENT_TENSOR_MIN_TOKENS
@@ -1126,7 +1128,7 @@ def latent_attention(q_eff: torch.Tensor, cache: torch.Tensor, block_tables: tor
         for s, (n, ctx) in enumerate(zip(step.q_lens, step.ctx_lens)):
             if n >= skip_from:
                 _latent_attention_portion(q_eff[t0:t0 + n], out[t0:t0 + n], cache, block_tables[s], heads, rank, D,
-                                          page_size, ctx, scale)
+                                          page_size, ctx, scale, win, sink_logit)
             t0 += n
         if all(n >= skip_from or (n == 1 and skip_single) for n in step.q_lens):
             return out
@@ -1153,30 +1155,44 @@ def latent_decode_splits(n_dec: int, head_groups: int, sm_count: int, max_kv_len
 
 
 def _latent_attention_portion(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
-                              heads: int, rank: int, D: int, page_size: int, ctx: int, scale: float) -> None:
-    """One request's portion of ``n`` tokens that follow ``ctx`` cached ones, on the tensor cores."""
+                              heads: int, rank: int, D: int, page_size: int, ctx: int, scale: float, window: int = 0,
+                              sink_logit: Optional[torch.Tensor] = None) -> None:
+    """One request's portion of ``n`` tokens that follow ``ctx`` cached ones, on the tensor cores.  With a window the
+    keys are gathered from the first one the portion's first query sees (rounded down to a multiple of 8: rows of 16
+    bytes), and a block of queries multiplies with the keys from its own first visible one up to its last position."""
     n = q.shape[0]
-    kv = ctx + n
+    first = max(0, ctx - window + 1) if window else 0        # the first key any query of the portion sees
+    start = first // 8 * 8
+    kv = ctx + n - start
     kv_pad = -(-kv // 8) * 8                      # rows of 16 bytes for the second product
-    rows = n * heads
     dev = q.device
     keys = torch.empty((kv_pad, D), dtype=q.dtype, device=dev)
     values_t = torch.empty((rank, 2 * kv_pad), dtype=q.dtype, device=dev)    # twice: for the weights' high and low parts
     with _prof.region("latent attention: gather rows", lambda: 2 * _nb(keys) + _nb(values_t)):
-        _check(lib().zi_latent_gather(_ptr(keys), _ptr(values_t), _ptr(cache), _tag(cache), _ptr(_i32(block_table, "block_table")),
-                                      page_size, kv, kv_pad, D, rank, _stream()), "latent_gather")
-    # in blocks of queries: a block multiplies with the keys up to its own last position only, so about
-    # five eighths of the rectangle of a whole prompt are computed instead of all of it
+        _check(lib().zi_latent_gather_from(_ptr(keys), _ptr(values_t), _ptr(cache), _tag(cache),
+                                           _ptr(_i32(block_table, "block_table")), page_size, kv, kv_pad, D, rank, start, first,
+                                           _stream()), "latent_gather")
+    # in blocks of queries: a block multiplies with the keys up to its own last position only (and from its first
+    # visible key on), so about five eighths of the rectangle of a whole prompt are computed instead of all of it
+    plain = not window and sink_logit is None
     for q0 in range(0, n, LATENT_QUERY_BLOCK):
         q1 = min(n, q0 + LATENT_QUERY_BLOCK)
         rows_b = (q1 - q0) * heads
-        kvb = min(kv_pad, -(-(ctx + q1) // 8) * 8)
-        scores = linear(q[q0:q1].view(rows_b, D), keys[:kvb], out_dtype=torch.float32, fresh_weight=True)
+        k0 = (max(0, ctx + q0 - window + 1) // 8 * 8 - start) if window else 0       # in rows of `keys`
+        k0 = max(k0, 0)
+        k1 = min(kv_pad, -(-(ctx + q1 - start) // 8) * 8)
+        kvb = k1 - k0
+        scores = linear(q[q0:q1].view(rows_b, D), keys[k0:k1], out_dtype=torch.float32, fresh_weight=True)
         probs = torch.empty((rows_b, 2 * kvb), dtype=q.dtype, device=dev)
         with _prof.region("latent attention: causal softmax", lambda: _nb(scores, probs)):
-            _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows_b), heads, ctx + q0,
-                                           kvb, ctypes.c_float(scale), _stream()), "causal_softmax")
-        linear(probs, values_t[:, :2 * kvb], out=out[q0:q1].view(rows_b, rank), fresh_weight=True)
+            if plain:
+                _check(lib().zi_causal_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows_b), heads, ctx + q0,
+                                               kvb, ctypes.c_float(scale), _stream()), "causal_softmax")
+            else:
+                _check(lib().zi_window_softmax(_ptr(probs), _ptr(scores), _tag(probs), ctypes.c_longlong(rows_b), heads, ctx + q0,
+                                               start + k0, kvb, window, ctypes.c_float(scale), _ptr(sink_logit), _stream()),
+                       "window_softmax")
+        linear(probs, values_t[:, 2 * k0:2 * k1], out=out[q0:q1].view(rows_b, rank), fresh_weight=True)
 
 
 # ----------------------------------------------------------------------- attention
@@ -1281,9 +1297,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     keep_first = int(keep_first or 0) if window else 0
     same_size = value_dim is None or int(value_dim) == head_dim
     # the tensor-core kernels take values of the keys' size; kept first tokens only in the form with a sink
-    changed = sink_logit is not None or softcap or dist_bias is not None
+    changed = sink_logit is not None or bool(softcap) or dist_bias is not None
     fast = ATTENTION_BACKEND != "generic" and q.dtype == torch.bfloat16 and same_size and (not keep_first or bool(sink)) \
-        and not changed
+        and not (changed and (sink or keep_first))
     dec_ok = fast and step.n_dec > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 1)
     pf_ok = fast and step.n_pf_tiles > 0 and L.zi_attention_mma_supported(num_heads, num_kv_heads, head_dim, 0) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
@@ -1299,6 +1315,30 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     win = int(window or 0)
     work = lambda decode: _attention_work(step, decode, num_heads, num_kv_heads, head_dim, q.element_size(), win, keep_first) \
         if _prof.ACTIVE is not None else (0, 0)
+    if changed:
+        # changed scores (a cap, a bias by distance, a learned sink): the mma.sync kernels' form with exact weights
+        _score_changes_ok(num_heads, sink_logit, dist_bias)
+        n_dist = dist_bias.shape[1] if dist_bias is not None else 0
+        if step.n_pf_tiles > 0:
+            with _prof.region("attention (prefill, mma.sync, changed scores)", *work(False)):
+                _check(L.zi_attention_prefill_mma_mods(
+                    _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                    block_tables.stride(0), _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(step.pf_tile_seq), _ptr(step.pf_tile_q0),
+                    step.n_pf_tiles, num_heads, num_kv_heads, head_dim, page_size, win, ctypes.c_float(scale),
+                    _ptr(sink_logit), ctypes.c_float(softcap), _ptr(dist_bias), n_dist, _stream()),
+                    "attention (prefill, changed scores)")
+        if step.n_dec > 0:
+            splits = decode_splits(step.n_dec, num_kv_heads, _sm_count(q.device), step.max_kv_len if not win else min(step.max_kv_len or win, win))
+            need = L.zi_attention_decode_workspace_floats(step.n_dec, num_heads, num_kv_heads, head_dim, splits)
+            ws = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+            with _prof.region("attention (decode, changed scores)", *work(True)):
+                _check(L.zi_attention_decode_mma_mods(
+                    _ptr(out), out.stride(0), _ptr(ws), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache),
+                    ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), block_tables.stride(0), _ptr(step.cu_q),
+                    _ptr(step.kv_lens), _ptr(step.dec_seq), step.n_dec, num_heads, num_kv_heads, head_dim, page_size, win,
+                    ctypes.c_float(scale), splits, _ptr(sink_logit), ctypes.c_float(softcap), _ptr(dist_bias), n_dist,
+                    _stream()), "attention (decode, changed scores)")
+        return out
     if sink:
         # a softmax with a sink: the mma.sync kernels' form whose weights meet the values as two bfloat16 parts (a design
         # that has a sink also wants its softmax weights in 32-bit) and whose denominator counts the sink
