@@ -24,7 +24,8 @@ With ``--design luvavik`` it runs another measurement instead and prints a JSON 
 sizes of real models (widths 2048 and 4096; ``--design-sizes``), beside Qwen3 dense at the same width,
 layer count and multiply-adds per token; ``--design rogosun`` does the same for the Rogosun design, beside
 Luvavik (the nearest design the engine has) and Qwen3, and ``--design vumezen`` for the Vumezen design, beside
-Rogosun (whose attention with a sink and routed experts beside a shared one are the nearest the engine has) and Qwen3; ``--profile PATH`` adds both models' per-kernel-class times and
+Rogosun (whose attention with a sink and routed experts beside a shared one are the nearest the engine has) and Qwen3, and
+``--design sepitar`` for the Sepitar design, beside Vumezen, Luvavik and Qwen3; ``--profile PATH`` adds both models' per-kernel-class times and
 roofline fractions.  The default workload and its output line are untouched.
 
 Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback
@@ -184,6 +185,30 @@ def vumezen_shape(width: int, heads: int, experts: int, top: int, expert_ff: int
             "max_position_embeddings": 8192}
 
 
+def sepitar_shape(width: int, heads: int, experts: int, top: int, expert_ff: int, dense_ff: int) -> dict:
+    """A Sepitar configuration with layers the size of a real model's: blocks with one norm whose two sublayers read it;
+    latent attention with heads of 128 + 64 rotated dimensions over a latent of 512, queries through a latent of 1,536,
+    a window of 1,024 tokens and a learned sink; attention with biases, a distance table and a gate per channel (heads
+    of 128, four query heads per kv head, a window of 1,024); attention with a norm over the whole of q and k, 64
+    rotated dimensions, a capped score, a sink and a gate per head, over all earlier keys; clamped gated experts chosen
+    by their logits beside a shared expert in every layer.  Five layers of which 1..2 run twice: seven layer runs."""
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "scale": 192 ** -0.5,
+                     "mask": {"size": 1024},
+                     "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                          "scale": 128 ** -0.5, "bias_max": 2048, "mask": {"size": 1024}}}
+    att2 = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                             "scale": 128 ** -0.5, "softcap": 50.0,
+                                             "rot": {"base": 1000000.0, "dims": 64,
+                                                     "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top}}
+    layers = [dict(lat, mlp=moe), dict(att, mlp=moe), dict(att2, mlp=moe), dict(lat, mlp=moe), dict(lat, mlp=moe)]
+    return {"architecture": "Sepitar", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "max_position_embeddings": 8192}
+
+
 DESIGN_SIZES = {
     # name: (width, heads, experts, chosen, expert ff, dense ff); Qwen3 beside it: the same width, layer runs and
     # heads of 128, a feed-forward as wide as the chosen experts together (equal products per token)
@@ -276,6 +301,15 @@ def compare_designs(args) -> int:
             results[f"vumezen_{size}"] = measure(f"vumezen_{size}", VumezenConfig.from_dict(own), own["vocab"])
             other = rogosun_shape(width, heads, experts, top, eff, dff)
             results[f"rogosun_{size}"] = measure(f"rogosun_{size}", RogosunConfig.from_dict(other), other["vocab"])
+        elif args.design == "sepitar":
+            # beside Vumezen (blocks whose sublayers read one stream, attention with a window and a sink on the same
+            # tensor-core kernels, experts beside a shared one), Luvavik (latent attention) and Qwen3
+            from zinfer_b200.config import SepitarConfig, VumezenConfig
+            own = sepitar_shape(width, heads, experts, top, eff, dff)
+            results[f"sepitar_{size}"] = measure(f"sepitar_{size}", SepitarConfig.from_dict(own), own["vocab"])
+            other = vumezen_shape(width, heads, experts, top, eff, dff)
+            results[f"vumezen_{size}"] = measure(f"vumezen_{size}", VumezenConfig.from_dict(other), other["vocab"])
+            results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
         else:
             results[f"luvavik_{size}"] = measure(f"luvavik_{size}", LuvavikConfig.from_dict(raw), raw["vocab"])
         # two products of an expert against three of the gated feed-forward: equal multiply-adds per token
@@ -286,7 +320,8 @@ def compare_designs(args) -> int:
     if args.profile:
         with open(args.profile, "w") as f:
             json.dump(profiles, f, indent=1)
-    names = {"rogosun": "Rogosun beside Luvavik and Qwen3 dense", "vumezen": "Vumezen beside Rogosun and Qwen3 dense"}.get(
+    names = {"rogosun": "Rogosun beside Luvavik and Qwen3 dense", "vumezen": "Vumezen beside Rogosun and Qwen3 dense",
+             "sepitar": "Sepitar beside Vumezen, Luvavik and Qwen3 dense"}.get(
         args.design, "Luvavik beside Qwen3 dense")
     print(json.dumps({"metric": f"prefill and decode tokens/s, {names} at equal width and layer runs",
                       "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
@@ -311,7 +346,7 @@ def main() -> int:
                     help="with ZINFER_B200_TRACE=1 in the environment: write the timeline of one decode step at the "
                          "headline batch (every kernel's start, the completion of what it depends on, and what it adds "
                          "to the chain) there as JSON, and do nothing else")
-    ap.add_argument("--design", default=None, choices=["luvavik", "rogosun", "vumezen"],
+    ap.add_argument("--design", default=None, choices=["luvavik", "rogosun", "vumezen", "sepitar"],
                     help="instead of the default benchmark: prefill and decode throughput of this design at layer sizes "
                          "of real models beside Qwen3 dense at equal size (a JSON line of its own)")
     ap.add_argument("--design-sizes", default=None, help="with --design: widths to run, e.g. 2048 or 2048,4096")

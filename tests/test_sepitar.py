@@ -462,6 +462,43 @@ def test_sizes_of_a_real_layer(tmp_path):
                             ("mixed", ru.trace_mixed(reqs, 2, max_live=3, tail=20))):
             ru.assert_close(ru.run_in_process(runner, trace), plain, what=f"real sizes/{mode}", argmax_frac=0.0, **TOL[dtype])
         runner.manager.check()
+        if dtype == torch.bfloat16:
+            # a prompt and a single token ran on the tensor-core kernels, not on the exact ones
+            from zinfer_b200 import profiling
+            from zinfer_b200.engine import StepEntry
+            with profiling.profile() as prof:
+                runner.step([StepEntry("p", reqs["r0"][:100], [99])])
+                runner.step([StepEntry("p", reqs["r0"][100:101], [0])])
+            runner.end_request("p")
+            ran = {c["class"] for c in prof.summary()["classes"]}
+            assert {"attention (prefill, mma.sync, changed scores)", "attention (decode, changed scores)",
+                    "latent attention (decode, split keys)", "latent attention: causal softmax"} <= ran, ran
+            assert not {"attention (exact, CUDA cores)", "latent attention (exact, CUDA cores)"} & ran, ran
+
+
+@gpu
+def test_fast_kernels_agree_with_the_exact_ones(tmp_path, monkeypatch):
+    """The same bfloat16 model on the tensor-core attention kernels and on the exact kernels: whole prompts, portions
+    and single tokens agree to the rounding of the softmax weights' second part."""
+    from zinfer_b200 import ops
+
+    cfg = U.config(131, 128, [
+        U.layer("attention", U.att(8, 2, 64, 64, 0.25, 70, 200), None),
+        U.layer("attention_2", U.att2(4, 4, 128, 128, 0.2, 8.0, 32), None),
+        U.layer("latent_attention", U.lat(20, 16, 16, 16, 48, 24, 0.4, 45), None),      # more heads than one block of the decode kernel takes
+    ], rel_rows={0: 24})
+    weights = U.make_weights(cfg, seed=81)
+    reqs = ru.make_requests(cfg["vocab"], [300, 130, 33], seed=2)
+    traces = (ru.trace_whole(reqs), ru.trace_tail_decode(reqs, 20), ru.trace_portions(reqs, 5, sizes=(64, 3, 129, 32, 1, 40)),
+              ru.trace_mixed(reqs, 4, max_live=3, tail=12))
+    got = {}
+    for backend in ("generic", "auto"):
+        monkeypatch.setattr(ops, "ATTENTION_BACKEND", backend)
+        runner = make_runner(tmp_path, cfg, weights, torch.bfloat16, DEV, page_size=16, max_tokens=640, max_requests=3)
+        got[backend] = [ru.run_in_process(runner, t) for t in traces]
+    for exact, fast in zip(got["generic"], got["auto"]):
+        for key, row in exact.items():
+            assert np.abs(fast[key] - row).max() <= 2e-2 * np.abs(row).max(), key
 
 
 @gpu
