@@ -317,11 +317,24 @@ struct ScoreMods {
   float scale;
 };
 constexpr float ZI_LOG2E = 1.4426950408889634f;
-__device__ __forceinline__ float changed_score(const ScoreMods& md, float dot, int head, int dist) {
+// tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast exponential (the softmax of these kernels uses the same one): absolute
+// error near 1e-7, which the cap multiplies.
+__device__ __forceinline__ float fast_tanh(float x) {
+  float t;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(x * (2.0f * ZI_LOG2E)));
+  return 1.0f - __fdividef(2.0f, t + 1.0f);
+}
+__device__ __forceinline__ float dist_bias_at(const ScoreMods& md, int head, int dist) {
+  return md.dist_bias ? __ldg(md.dist_bias + (size_t)head * md.n_dist + min(max(dist, 0), md.n_dist - 1)) : 0.f;
+}
+// the changed score in the exp2 domain, from the dot product and the bias already fetched
+__device__ __forceinline__ float changed_score(const ScoreMods& md, float dot, float bias) {
   float v = dot * md.scale;
-  if (md.softcap > 0.f) v = md.softcap * tanhf(v / md.softcap);
-  if (md.dist_bias) v += md.dist_bias[(size_t)head * md.n_dist + min(max(dist, 0), md.n_dist - 1)];
-  return v * ZI_LOG2E;
+  if (md.softcap > 0.f) v = md.softcap * fast_tanh(v * __fdividef(1.0f, md.softcap));
+  return (v + bias) * ZI_LOG2E;
+}
+__device__ __forceinline__ float changed_score(const ScoreMods& md, float dot, int head, int dist) {
+  return changed_score(md, dot, dist_bias_at(md, head, dist));
 }
 
 template <int D> struct DecodeCfg { static constexpr int STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2); };
@@ -652,6 +665,23 @@ __device__ __forceinline__ void attn_decode_unit(
       pg_next = lookup(tt + 1);
       if (tt < n_tiles) issue(tt, pg);
     }
+    // a bias by distance is asked for before the tile is waited for, so that its trip to memory passes under that wait
+    float bias_pre[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if constexpr (MD) {
+      if (md->dist_bias) {
+        const int k0p = tile_key0(t_begin + t) + warp * DC_KEYS;
+        if constexpr (TR) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            bias_pre[c] = dist_bias_at(*md, kvh * g + min(2 * (lane & 3) + (c & 1), g - 1), pos - (k0p + (lane >> 2) + (c >> 1) * 8));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            bias_pre[c] = dist_bias_at(*md, kvh * g + min((lane >> 2) + ((c & 3) >> 1) * 8, g - 1),
+                                       pos - (k0p + (c >> 2) * 8 + 2 * (lane & 3) + (c & 1)));
+        }
+      }
+    }
     if constexpr (TMA) {
       // the tile's bytes have landed when its barrier's phase completes (bounded wait)
       if (!mbar_wait(&my_bars[t % STAGES], (uint32_t)(t / STAGES) & 1u)) {
@@ -674,10 +704,7 @@ __device__ __forceinline__ void attn_decode_unit(
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = st[c] * scale_log2;
-          if constexpr (MD) {
-            const int j = key0 + (lane >> 2) + (c >> 1) * 8;
-            v = changed_score(*md, st[c], kvh * g + min(2 * (lane & 3) + (c & 1), g - 1), pos - j);
-          }
+          if constexpr (MD) v = changed_score(*md, st[c], bias_pre[c]);
           if (need_mask) {
             const int j = key0 + (lane >> 2) + (c >> 1) * 8;
             if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;
@@ -728,10 +755,7 @@ __device__ __forceinline__ void attn_decode_unit(
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float v = s[nt][c] * scale_log2;
-          if constexpr (MD) {
-            const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
-            v = changed_score(*md, s[nt][c], kvh * g + min((lane >> 2) + (c >> 1) * 8, g - 1), pos - j);
-          }
+          if constexpr (MD) v = changed_score(*md, s[nt][c], bias_pre[nt * 4 + c]);
           if (need_mask) {
             const int j = key0 + nt * 8 + 2 * (lane & 3) + (c & 1);
             if (j >= kv_hi || (j < kv_lo && j >= keep_end)) v = -INFINITY;

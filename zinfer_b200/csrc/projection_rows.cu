@@ -10,7 +10,9 @@
 #include "common.cuh"
 
 namespace {
-constexpr int ROW_THREADS = 256;
+// few tokens in bfloat16 (a decode step): more threads a token, since the walk is latency; the 32-bit path keeps one
+// block size, so that its sums' order depends on nothing but the row
+constexpr int ROW_THREADS = 256, ROW_THREADS_FEW = 1024;
 
 template <typename TS>
 __device__ __forceinline__ float row_at(const TS* x, const float* bias, int e) {
@@ -50,7 +52,7 @@ __device__ __forceinline__ void finish_part(const TS* x, const float* bias, int 
 }
 
 template <typename TS, typename T>
-__global__ void __launch_bounds__(ROW_THREADS)
+__global__ void __launch_bounds__(ROW_THREADS_FEW)
 qkv_rows_kernel(const TS* __restrict__ src, int src_stride, const float* __restrict__ bias, T* __restrict__ q_out,
                 int q_stride, T* __restrict__ gate_out, int gate_stride, int n_gate, int nq, int nkv, int d, int dv,
                 const float* __restrict__ qw, const float* __restrict__ kw, float eps, int rot_dims,
@@ -125,7 +127,8 @@ extern "C" int zi_qkv_rows_prepare(const void* src, int src_dtype, int src_strid
   if (!kcache || !vcache || !slots || page_size <= 0) return zi_refuse("qkv_rows_prepare: keys and values need pages and slots");
   if (n_gate < 0 || (n_gate > 0 && !gate_out)) return zi_refuse("qkv_rows_prepare: %d gate columns without a place", n_gate);
   ZI_DISPATCH_SRC_OUT(src_dtype, out_dtype, TS, TT,
-                      zi_launch(qkv_rows_kernel<TS, TT>, dim3(T), dim3(ROW_THREADS), 0, stream, (const TS*)src, src_stride, bias,
+                      zi_launch(qkv_rows_kernel<TS, TT>, dim3(T), dim3(T <= 64 && out_dtype == ZI_BF16 ? ROW_THREADS_FEW : ROW_THREADS), 0, stream,
+                                (const TS*)src, src_stride, bias,
                                 (TT*)q_out, q_stride, (TT*)gate_out, gate_stride, n_gate, nq, nkv, d, dv, qw, kw, eps, rot_dims,
                                 cos_t, sin_t, n_table_pos, positions, (TT*)kcache, (TT*)vcache, slots, page_size));
   return zi_check_launch("qkv_rows_prepare");
