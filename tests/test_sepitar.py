@@ -546,3 +546,81 @@ def test_replay_program(tmp_path, models):
     got = ru.run_trace_tool(d, "float32", trace, str(tmp_path / "out"), ru.max_live_tokens(trace), cfg["vocab"], info=info)
     ru.assert_close(got, plain, what="trace_run", argmax_frac=0.0, **TOL[torch.float32])
     assert info["pages_reused"] and info["pages_reused"] > 0
+
+
+# ------------------------------------------------------------------ the new kernels alone, against their plain stand-ins
+@gpu
+def test_row_kernels_against_plain_arithmetic():
+    """zi_qkv_rows_prepare, zi_rmsnorm_rows, zi_latent_prepare_rows, zi_rope_table_freqs: each against a few lines of PyTorch,
+    for 32-bit sources beside 16-bit results and for one type throughout, few rows (the wide form) and many."""
+    import kernel_refs as R
+    from zinfer_b200 import ops
+
+    g = torch.Generator(device=DEV).manual_seed(5)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=DEV)
+    freqs = torch.tensor([1.0, 0.31, 0.07, 0.002], device=DEV)
+    cos, sin = ops.rope_table_freqs(300, freqs, 1.25)
+    rc, rs = R.rope_table_freqs(300, freqs, 1.25)
+    assert torch.allclose(cos, rc, atol=1e-6) and torch.allclose(sin, rs, atol=1e-6)
+    for T, out_dtype in ((5, torch.bfloat16), (200, torch.bfloat16), (7, torch.float32)):
+        nq, nkv, d, dv, n_gate, page, rot = 6, 2, 12, 20, 6, 8, 8
+        width = nq * d + nkv * d + nkv * dv + n_gate
+        proj = rnd(T, width)
+        bias, qw, kw = rnd(width) * 0.3, 1 + 0.2 * rnd(nq * d), 1 + 0.2 * rnd(nkv * d)
+        pos = torch.randint(0, 300, (T,), generator=g, device=DEV, dtype=torch.int32)
+        slots = torch.randperm(40 * page, generator=g, device=DEV)[:T].to(torch.int32)
+        slots[0] = -1                                                   # a row that pads a captured batch writes nothing
+        caches = [[torch.zeros(40, nkv, page, n, dtype=out_dtype, device=DEV) for n in (d, dv)] for _ in range(2)]
+        got = ops.qkv_rows_prepare(proj, bias, nq, nkv, d, dv, n_gate, qw, kw, 1e-5, rot, cos, sin, pos, *caches[0], slots, page, out_dtype)
+        want = R.qkv_rows_prepare(proj, bias, nq, nkv, d, dv, n_gate, qw, kw, 1e-5, rot, cos, sin, pos, *caches[1], slots, page, out_dtype)
+        tol = dict(rtol=2e-2, atol=2e-2) if out_dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+        for a, b in zip((*got, *caches[0]), (*want, *caches[1])):
+            assert torch.allclose(a.float(), b.float(), **tol)
+        assert caches[0][0].abs().sum() > 0
+        x = rnd(T, 50)[:, 3:40]                                         # a view of wider rows
+        w = 1 + 0.2 * rnd(37)
+        assert torch.allclose(ops.rmsnorm_rows(x, w, 1e-6, out_dtype).float(), R.rmsnorm_rows(x, w, 1e-6, out_dtype).float(), **tol)
+        for neighbours in (False, True):
+            heads, dim, rd, rank = 3, 10, 8, 14
+            D = rank + rd
+            q, kv, cw = rnd(T, heads * (dim + rd)).to(out_dtype), rnd(T, D + 5), 1 + 0.2 * rnd(rank)
+            outs = []
+            for fn in (ops.latent_prepare_rows, R.latent_prepare_rows):
+                q_eff = torch.zeros(T, heads, D, dtype=out_dtype, device=DEV)
+                cache = torch.zeros(40, 1, page, D, dtype=out_dtype, device=DEV)
+                fn(q, kv, heads, dim, rd, rank, rd, neighbours, cw, 1e-5, cos, sin, pos, q_eff, cache, slots)
+                outs.append((q_eff[:, :, rank:].float(), cache.float()))
+            assert all(torch.allclose(a, b, **tol) for a, b in zip(*outs))
+
+
+@gpu
+def test_clamped_gate_grouped_gate_and_the_logits_router():
+    import kernel_refs as R
+    from zinfer_b200 import ops
+
+    g = torch.Generator(device=DEV).manual_seed(6)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=DEV)
+    for T, I, dtype in ((3, 24, torch.bfloat16), (130, 64, torch.bfloat16), (9, 7, torch.float32), (40, 16, torch.float32)):
+        gu = (3.0 * rnd(T, 2 * I)).to(dtype)
+        tol = dict(rtol=2e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-6)
+        got, want = ops.clamped_gate(gu, 1.5, 1.702, 1.0, dtype), R.clamped_gate(gu, 1.5, 1.702, 1.0, dtype)
+        assert torch.allclose(got.float(), want.float(), **tol) and want.float().abs().max() > 1.0
+        parts = ops.Partials(torch.stack([gu.float() * 0.25, gu.float() * 0.75]).contiguous())       # split-K partial sums, added in order
+        assert torch.allclose(ops.clamped_gate(parts, 1.5, 1.702, 1.0, dtype).float(), want.float(), **tol)
+        x, gate = rnd(T, 4 * I).to(dtype), rnd(T, 4).to(dtype)
+        assert torch.allclose(ops.sigmoid_gate(x, gate, group=I).float(), R.sigmoid_gate(x, gate, group=I).float(), **tol)
+    for T, K, NR, top in ((1, 64, 8, 4), (70, 192, 5, 5), (9, 33, 12, 1)):
+        x, w, b = rnd(T, K).to(torch.bfloat16), rnd(NR, K).to(torch.bfloat16), rnd(NR)
+        w[1] = w[0]                                                      # equal logits unless the bias parts them
+        b[1] = b[0]                                                      # a tie: the earlier expert first
+        chosen, weight = ops.moe_router_top_logits(x, w, b, top)
+        rc, rw = R.moe_router_top_logits(x, w, b, top)
+        z = x.float() @ w.float().T + b
+        for t in range(T):
+            # the same experts in the same order wherever the logits are clearly apart
+            gaps = z[t].sort(descending=True).values
+            clear = all(float(gaps[k] - gaps[k + 1]) > 1e-3 or float(gaps[k] - gaps[k + 1]) == 0.0 for k in range(min(top, NR - 1)))
+            if clear:
+                assert chosen[t].tolist() == rc[t].tolist(), (t, chosen[t], rc[t])
+                assert torch.allclose(weight[t], rw[t], rtol=1e-4, atol=1e-6)
+        assert torch.allclose(weight.sum(-1), torch.ones(T, device=DEV), atol=1e-5)
